@@ -1,0 +1,109 @@
+"""Seeded synthetic inputs with the shapes and value distributions of the BEVFormer-DFA3D operator.
+
+They stand in for the nuScenes-derived tensors the reference feeds its op (camera features, depth
+distributions and projected BEV reference points): shapes come from the reference's configs
+(BEVFormer_DFA3D/projects/configs/bevformer/bevformer_base_DFA3D.py: 256-d, 8 heads, 4 levels,
+8 points, 200x200 BEV; 900x1600 images at strides 8/16/32/64 -> 116x200 ... 15x25, the same level
+sizes as unittest_DFA3D.py:46-50).  Everything is drawn from a CPU ``torch.Generator`` so that the CPU
+checker and the GPU see identical bits.
+"""
+from dataclasses import dataclass, field
+from typing import List, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class Workload:
+    name: str
+    B: int                                   # batch * cameras
+    levels: Tuple[Tuple[int, int], ...]      # (h, w) per level
+    D: int                                   # depth bins
+    Q: int                                   # queries per camera
+    P: int                                   # sampling points per level
+    H: int = 8                               # heads
+    C: int = 32                              # channels per head
+    seed: int = 0
+    oob: bool = False                        # ~15 % of points with x or y outside [0,1]
+    value_dtype: str = "fp32"                # "fp32" | "bf16" (value and dist storage)
+
+    @property
+    def L(self):
+        return len(self.levels)
+
+    @property
+    def N(self):
+        return sum(h * w for h, w in self.levels)
+
+    @property
+    def points(self):
+        """Sampled points = B*Q*H*L*P (the unit of the throughput metric)."""
+        return self.B * self.Q * self.H * self.L * self.P
+
+    def with_(self, **kw):
+        d = dict(self.__dict__)
+        d.update(kw)
+        return Workload(**d)
+
+    def algorithmic_bytes(self):
+        """Compulsory HBM traffic (forward, backward): every input read once, every output written
+        once, dist counted un-repeated (B,N,D), depth_score not materialised, no memset traffic."""
+        e = 2 if self.value_dtype == "bf16" else 4
+        pts = self.points
+        value = self.B * self.N * self.H * self.C
+        dist = self.B * self.N * self.D
+        out = self.B * self.Q * self.H * self.C * 4
+        fwd = value * e + dist * e + pts * 16 + out
+        bwd = out + value * e + dist * e + pts * 16 + value * 4 + dist * 4 + pts * 16
+        return fwd, bwd
+
+
+_BASE_LEVELS = ((116, 200), (58, 100), (29, 50), (15, 25))
+
+WORKLOADS = {
+    # BASELINE.json configs[0..3]; configs[4] (encoder stack) reuses cfg2's op shapes with D=118.
+    "cfg0": Workload("cfg0", B=1, levels=((32, 32), (16, 16)), D=16, Q=512, P=4, seed=0),
+    "cfg1": Workload("cfg1", B=6, levels=((23, 40),), D=64, Q=6000, P=8, seed=1),
+    "cfg2": Workload("cfg2", B=6, levels=_BASE_LEVELS, D=64, Q=10000, P=8, seed=2, oob=True),
+    "cfg3": Workload("cfg3", B=6, levels=_BASE_LEVELS, D=64, Q=10000, P=8, seed=3, oob=True,
+                     value_dtype="bf16"),
+    "cfg4op": Workload("cfg4op", B=6, levels=_BASE_LEVELS, D=118, Q=10000, P=8, seed=4, oob=True),
+    # small cases for parity tests
+    "tiny": Workload("tiny", B=2, levels=((5, 7), (3, 4)), D=5, Q=6, P=3, H=2, C=8, seed=11, oob=True),
+    "odd": Workload("odd", B=3, levels=((9, 6), (4, 5), (2, 2)), D=7, Q=33, P=5, H=3, C=16, seed=12,
+                    oob=True),
+}
+
+
+def level_tensors(w: Workload, device="cpu"):
+    """(spatial_shapes_3D (L,3) int64 = (h,w,D), level_start_index (L) int64)."""
+    shapes = torch.tensor([[h, ww, w.D] for h, ww in w.levels], dtype=torch.int64)
+    hw = shapes[:, 0] * shapes[:, 1]
+    lsi = torch.cat([hw.new_zeros(1), hw.cumsum(0)[:-1]])
+    return shapes.to(device), lsi.to(device)
+
+
+def make_inputs(w: Workload, seed=None, head_repeat=False):
+    """CPU fp32 tensors: value (B,N,H,C), dist (B,N,D) [or (B,N,H,D) repeated over heads, the form the
+    reference op needs], loc (B,Q,H,L,P,3), attn (B,Q,H,L,P), grad_out (B,Q,H*C), shapes, lsi.
+
+    value ~ N(0,1); dist = softmax over D of N(0,1); x,y ~ U(0,1) (or U(-0.0423,1.0423): each axis in
+    range with probability 0.922, so ~15 % of points leave the image); z ~ U(0,1);
+    attn = softmax over L*P of N(0,1); grad_out ~ N(0,1).  With value_dtype == "bf16", value and dist
+    are rounded to bf16 once (and returned as fp32 holding the rounded values)."""
+    g = torch.Generator().manual_seed(w.seed if seed is None else seed)
+    value = torch.randn(w.B, w.N, w.H, w.C, generator=g)
+    dist = torch.randn(w.B, w.N, w.D, generator=g).softmax(-1)
+    loc = torch.rand(w.B, w.Q, w.H, w.L, w.P, 3, generator=g)
+    if w.oob:
+        loc[..., :2] = loc[..., :2] * 1.0846 - 0.0423
+    attn = torch.randn(w.B, w.Q, w.H, w.L * w.P, generator=g).softmax(-1).view(w.B, w.Q, w.H, w.L, w.P)
+    grad_out = torch.randn(w.B, w.Q, w.H * w.C, generator=g)
+    if w.value_dtype == "bf16":
+        value = value.bfloat16().float()
+        dist = dist.bfloat16().float()
+    if head_repeat:
+        dist = dist.view(w.B, w.N, 1, w.D).repeat(1, 1, w.H, 1)
+    shapes, lsi = level_tensors(w)
+    return dict(value=value, dist=dist, loc=loc, attn=attn, grad_out=grad_out,
+                shapes=shapes, lsi=lsi)
