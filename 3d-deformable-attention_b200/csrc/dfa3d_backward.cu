@@ -1,0 +1,368 @@
+// DFA3D backward kernels (sm_100a).
+//
+// Same decomposition as the forward: one warp per (camera, query, head) item, lane j owns sampling
+// point j of a 32-point chunk.  Per chunk:
+//   prologue -- the lane recomputes its point's geometry and per-corner depth scores from `dist`
+//               (fused mode; the (B,Q,H,L,P,4) depth_score tensor is never read back) and publishes
+//               {row offset, a * bilinear * depth score} per corner in shared memory;
+//   rows     -- a group of G lanes reads one value row (16-byte loads), takes its dot product with
+//               the item's grad_out row (xor-shuffles inside the group) and adds
+//               weight * grad_out to grad_value with one 16-byte vector reduction per lane
+//               (red.global.add.v4.f32) instead of one scalar atomic per channel;
+//   epilogue -- the four dot products t_k of a point return to its owner lane through shared
+//               memory; grad_attn, grad_loc (x, y and, fused, z), grad_depth_score and the grad_dist
+//               atomics all follow from t_k and the quantities the lane already holds.
+// No block-wide barrier and no serial thread-0 reduction remain
+// (cf. wms_deform_attn_cuda_kernel.cuh:378-407, ms_depth_score_sample_cuda_kernel.cuh:301-319).
+#include "dfa3d_common.cuh"
+#include "dfa3d_launch.h"
+
+namespace dfa3d {
+
+enum BwdMode { kFusedBwd = 0, kGivenDepthScoreBwd = 1 };
+
+struct __align__(8) RowEntryB {
+  int off;
+  float wgt;
+};
+
+// Per-lane state of one sampling point that the epilogue needs.
+struct PointState {
+  PointGeo g;
+  float aw;
+  float bw[4], ds[4];
+  float lo[4], hi[4];   // depth-distribution values at z0 / z0+1 per corner (fused mode)
+  bool live;            // j < LP && ok2
+};
+
+template <typename DT, int MODE>
+__device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, long long item, int j,
+                                          int b, int h, PointState &s, float (&wgt)[4],
+                                          int (&off)[4]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    s.ds[k] = 0.f; s.bw[k] = 0.f; s.lo[k] = 0.f; s.hi[k] = 0.f; wgt[k] = 0.f; off[k] = -1;
+    s.g.pix[k] = -1;
+  }
+  s.live = false; s.aw = 0.f; s.g.ok2 = false; s.g.ok3 = false;
+  if (j >= a.LP) return;
+  const int l = j / a.P;
+  const long long pt = item * a.LP + j;
+  const float *lp = a.loc + pt * a.loc_stride;
+  const float x = __ldg(lp), y = __ldg(lp + 1);
+  const float z = (MODE == kFusedBwd) ? __ldg(lp + 2) : 0.f;
+  s.aw = __ldg(a.attn + pt);
+  s.g = point_geometry(x, y, z, MODE == kFusedBwd, lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N);
+  if (!s.g.ok2) return;
+  s.live = true;
+  bilinear_weights(s.g, s.bw);
+  if (MODE == kFusedBwd) {
+    const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
+                        (long long)b * a.N * a.dist_pix_stride + (long long)h * a.dist_head_stride;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      load_depth_pair(dist_bh, a.dist_pix_stride, s.g.pix[k], s.g.z0, s.g.Dd, a.D, s.g.ok3, s.lo[k],
+                      s.hi[k]);
+    const float hd = 1.f - s.g.ld;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s.ds[k] = s.g.ok3 ? s.lo[k] * hd + s.hi[k] * s.g.ld : 0.f;
+  } else {
+    const float4 t = __ldg(reinterpret_cast<const float4 *>(a.ds_in) + pt);
+    s.ds[0] = s.g.pix[0] >= 0 ? t.x : 0.f;
+    s.ds[1] = s.g.pix[1] >= 0 ? t.y : 0.f;
+    s.ds[2] = s.g.pix[2] >= 0 ? t.z : 0.f;
+    s.ds[3] = s.g.pix[3] >= 0 ? t.w : 0.f;
+  }
+  const int row = a.H * a.C;
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (s.g.pix[k] >= 0) {
+      off[k] = s.g.pix[k] * row;
+      wgt[k] = s.aw * (s.bw[k] * s.ds[k]);
+    }
+}
+
+// Everything that follows from the four dot products t[k] = <value row k, grad_out row>.
+template <typename DT, int MODE>
+__device__ __forceinline__ void bwd_point_epilogue(const KArgs &a, long long item, int j, int b, int h,
+                                                   const PointState &s, const float (&t)[4]) {
+  if (j >= a.LP) return;
+  const long long pt = item * a.LP + j;
+  float g_attn = 0.f, g_x = 0.f, g_y = 0.f, g_z = 0.f;
+  float gds[4] = {0.f, 0.f, 0.f, 0.f};
+  if (s.live) {
+    const float hw = 1.f - s.g.lw, hh = 1.f - s.g.lh;
+    float tt[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) tt[k] = s.g.pix[k] >= 0 ? t[k] : 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      g_attn = fmaf(s.bw[k] * s.ds[k], tt[k], g_attn);
+      gds[k] = s.g.pix[k] >= 0 ? s.aw * (s.bw[k] * tt[k]) : 0.f;
+    }
+    const float e0 = s.ds[0] * tt[0], e1 = s.ds[1] * tt[1], e2 = s.ds[2] * tt[2], e3 = s.ds[3] * tt[3];
+    g_x = (float)s.g.W * s.aw * (hh * (e1 - e0) + s.g.lh * (e2 - e3));
+    g_y = (float)s.g.Hh * s.aw * (hw * (e3 - e0) + s.g.lw * (e2 - e1));
+    if (MODE == kFusedBwd && s.g.ok3) {
+      float *gd_bh = a.grad_dist + (long long)b * a.N * a.dist_pix_stride +
+                     (long long)h * a.dist_head_stride;
+      const float hd = 1.f - s.g.ld;
+      const bool zlo = s.g.z0 >= 0 && s.g.z0 < a.D;
+      const bool zhi = s.g.z0 + 1 <= s.g.Dd - 1 && s.g.z0 + 1 < a.D;
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (s.g.pix[k] >= 0) {
+          float *p = gd_bh + (long long)s.g.pix[k] * a.dist_pix_stride + s.g.z0;
+          if (gds[k] != 0.f) {
+            if (zlo) red_add(p, hd * gds[k]);
+            if (zhi) red_add(p + 1, s.g.ld * gds[k]);
+          }
+          acc = fmaf(gds[k], s.hi[k] - s.lo[k], acc);
+        }
+      }
+      g_z = (float)s.g.Dd * acc;
+    }
+  }
+  a.grad_attn[pt] = g_attn;
+  float *gl = a.grad_loc + pt * a.loc_stride;
+  gl[0] = g_x;
+  gl[1] = g_y;
+  if (MODE == kFusedBwd) gl[2] = g_z;
+  if (a.grad_ds_out)
+    reinterpret_cast<float4 *>(a.grad_ds_out)[pt] = make_float4(gds[0], gds[1], gds[2], gds[3]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// fused / given-depth-score backward, C a power of two with 16-byte row fragments
+// ------------------------------------------------------------------------------------------------
+template <typename VT, typename DT, int C, int MODE>
+__global__ void __launch_bounds__(kThreads)
+dfa3d_backward_kernel(const KArgs a) {
+  constexpr int V = RowVec<VT>::kElems;
+  constexpr int G = C / V;
+  constexpr int R = 32 / G;
+  constexpr int U = 4;
+
+  __shared__ LevelTable lv;
+  __shared__ RowEntryB rows[kWarpsPerCta][128];
+  __shared__ __align__(16) float dots[kWarpsPerCta][128];
+  stage_levels(lv, a);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * kWarpsPerCta + warp;
+  if (item >= a.items) return;
+  const int h = (int)(item % a.H);
+  const int b = (int)(item / ((long long)a.Q * a.H));
+  const int sub = lane % G, grp = lane / G;
+  const long long slice = ((long long)b * a.N * a.H + h) * C + sub * V;
+  const VT *vbase = reinterpret_cast<const VT *>(a.value) + slice;
+  float *gvbase = a.grad_value + slice;
+  RowEntryB *my = rows[warp];
+  float *myd = dots[warp];
+
+  float go[V];
+  {
+    const float *gp = a.grad_out + item * C + sub * V;
+#pragma unroll
+    for (int i = 0; i < V; i += 4) {
+      const float4 t = __ldg(reinterpret_cast<const float4 *>(gp + i));
+      go[i] = t.x; go[i + 1] = t.y; go[i + 2] = t.z; go[i + 3] = t.w;
+    }
+  }
+
+  for (int chunk = 0; chunk < a.LP; chunk += 32) {
+    PointState st;
+    float wgt[4];
+    int off[4];
+    bwd_point<DT, MODE>(a, lv, item, chunk + lane, b, h, st, wgt, off);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) my[lane * 4 + k] = RowEntryB{off[k], wgt[k]};
+    __syncwarp();
+    const int nrows = min(32, a.LP - chunk) * 4;
+    for (int r0 = 0; r0 < nrows; r0 += R * U) {
+      RowEntryB e[U];
+      float v[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int r = r0 + u * R + grp;
+        e[u] = (r < nrows) ? my[r] : RowEntryB{-1, 0.f};
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (e[u].off >= 0) {
+          RowVec<VT>::load(vbase + e[u].off, v[u]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) v[u][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) d = fmaf(v[u][i], go[i], d);
+#pragma unroll
+        for (int s = 1; s < G; s <<= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
+        const int r = r0 + u * R + grp;
+        if (sub == 0 && r < nrows) myd[r] = d;
+        if (e[u].off >= 0 && e[u].wgt != 0.f) {
+          float *gp = gvbase + e[u].off;
+#pragma unroll
+          for (int i = 0; i < V; i += 4)
+            red_add_v4(gp + i, e[u].wgt * go[i], e[u].wgt * go[i + 1], e[u].wgt * go[i + 2],
+                       e[u].wgt * go[i + 3]);
+        }
+      }
+    }
+    __syncwarp();
+    const float4 tq = reinterpret_cast<const float4 *>(myd)[lane];
+    const float t[4] = {tq.x, tq.y, tq.z, tq.w};
+    bwd_point_epilogue<DT, MODE>(a, item, chunk + lane, b, h, st, t);
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// any C: lanes stride over channels (correctness path for unusual widths)
+// ------------------------------------------------------------------------------------------------
+template <typename VT, typename DT, int MODE>
+__global__ void __launch_bounds__(kThreads)
+dfa3d_backward_generic_kernel(const KArgs a) {
+  __shared__ LevelTable lv;
+  __shared__ RowEntryB rows[kWarpsPerCta][128];
+  __shared__ __align__(16) float dots[kWarpsPerCta][128];
+  stage_levels(lv, a);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * kWarpsPerCta + warp;
+  if (item >= a.items) return;
+  const int C = a.C;
+  const int h = (int)(item % a.H);
+  const int b = (int)(item / ((long long)a.Q * a.H));
+  const long long slice = ((long long)b * a.N * a.H + h) * C;
+  const VT *vbase = reinterpret_cast<const VT *>(a.value) + slice;
+  float *gvbase = a.grad_value + slice;
+  const float *gop = a.grad_out + item * C;
+  RowEntryB *my = rows[warp];
+  float *myd = dots[warp];
+  for (int chunk = 0; chunk < a.LP; chunk += 32) {
+    PointState st;
+    float wgt[4];
+    int off[4];
+    bwd_point<DT, MODE>(a, lv, item, chunk + lane, b, h, st, wgt, off);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) my[lane * 4 + k] = RowEntryB{off[k], wgt[k]};
+    __syncwarp();
+    const int nrows = min(32, a.LP - chunk) * 4;
+    for (int r = 0; r < nrows; ++r) {
+      const RowEntryB e = my[r];
+      float d = 0.f;
+      if (e.off >= 0) {
+        for (int c = lane; c < C; c += 32) {
+          const float g = __ldg(gop + c);
+          d = fmaf(load_scalar(vbase + e.off + c), g, d);
+          if (e.wgt != 0.f) red_add(gvbase + e.off + c, e.wgt * g);
+        }
+      }
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
+      if (lane == 0) myd[r] = d;
+    }
+    __syncwarp();
+    const float4 tq = reinterpret_cast<const float4 *>(myd)[lane];
+    const float t[4] = {tq.x, tq.y, tq.z, tq.w};
+    bwd_point_epilogue<DT, MODE>(a, item, chunk + lane, b, h, st, t);
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// depth-score backward alone (two-stage API): one thread per sampling point
+// ------------------------------------------------------------------------------------------------
+template <typename DT>
+__global__ void __launch_bounds__(kThreads)
+dfa3d_depth_score_backward_kernel(const KArgs a) {
+  __shared__ LevelTable lv;
+  stage_levels(lv, a);
+  const long long npts = a.items * a.LP;
+  for (long long pt = (long long)blockIdx.x * blockDim.x + threadIdx.x; pt < npts;
+       pt += (long long)gridDim.x * blockDim.x) {
+    const long long item = pt / a.LP;
+    const int j = (int)(pt - item * a.LP);
+    const int l = j / a.P;
+    const int h = (int)(item % a.H);
+    const int b = (int)(item / ((long long)a.Q * a.H));
+    const float *lp = a.loc + pt * 3;
+    const PointGeo g = point_geometry(__ldg(lp), __ldg(lp + 1), __ldg(lp + 2), true, lv.h[l], lv.w[l],
+                                      lv.d[l], lv.start[l], a.N);
+    float g_z = 0.f;
+    if (g.ok3) {
+      const long long bh = (long long)b * a.N * a.dist_pix_stride + (long long)h * a.dist_head_stride;
+      const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) + bh;
+      float *gd_bh = a.grad_dist + bh;
+      const float4 gq = __ldg(reinterpret_cast<const float4 *>(a.grad_ds_in) + pt);
+      const float gds[4] = {gq.x, gq.y, gq.z, gq.w};
+      const float hd = 1.f - g.ld;
+      const bool zlo = g.z0 >= 0 && g.z0 < a.D;
+      const bool zhi = g.z0 + 1 <= g.Dd - 1 && g.z0 + 1 < a.D;
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (g.pix[k] >= 0) {
+          float lo, hi;
+          load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, g.Dd, a.D, true, lo, hi);
+          float *p = gd_bh + (long long)g.pix[k] * a.dist_pix_stride + g.z0;
+          if (zlo) red_add(p, hd * gds[k]);
+          if (zhi) red_add(p + 1, g.ld * gds[k]);
+          acc = fmaf(gds[k], hi - lo, acc);
+        }
+      }
+      g_z = (float)g.Dd * acc;
+    }
+    float *gl = a.grad_loc + pt * 3;
+    gl[0] = 0.f; gl[1] = 0.f; gl[2] = g_z;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side dispatch
+// ------------------------------------------------------------------------------------------------
+template <typename VT, typename DT, int MODE>
+static cudaError_t launch_backward_vd(const KArgs &a, cudaStream_t s) {
+  const unsigned grid = (unsigned)((a.items + kWarpsPerCta - 1) / kWarpsPerCta);
+  constexpr int V = RowVec<VT>::kElems;
+  const int g = (a.C % V == 0) ? a.C / V : 0;
+  switch (g) {
+    case 2:  dfa3d_backward_kernel<VT, DT, 2 * V, MODE><<<grid, kThreads, 0, s>>>(a); break;
+    case 4:  dfa3d_backward_kernel<VT, DT, 4 * V, MODE><<<grid, kThreads, 0, s>>>(a); break;
+    case 8:  dfa3d_backward_kernel<VT, DT, 8 * V, MODE><<<grid, kThreads, 0, s>>>(a); break;
+    case 16: dfa3d_backward_kernel<VT, DT, 16 * V, MODE><<<grid, kThreads, 0, s>>>(a); break;
+    default: dfa3d_backward_generic_kernel<VT, DT, MODE><<<grid, kThreads, 0, s>>>(a); break;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_backward(const KArgs &a, bool value_bf16, bool dist_bf16, bool given_ds,
+                            cudaStream_t s) {
+  if (a.items == 0) return cudaSuccess;
+  if (given_ds) {
+    return value_bf16 ? launch_backward_vd<__nv_bfloat16, float, kGivenDepthScoreBwd>(a, s)
+                      : launch_backward_vd<float, float, kGivenDepthScoreBwd>(a, s);
+  }
+  if (value_bf16)
+    return dist_bf16 ? launch_backward_vd<__nv_bfloat16, __nv_bfloat16, kFusedBwd>(a, s)
+                     : launch_backward_vd<__nv_bfloat16, float, kFusedBwd>(a, s);
+  return dist_bf16 ? launch_backward_vd<float, __nv_bfloat16, kFusedBwd>(a, s)
+                   : launch_backward_vd<float, float, kFusedBwd>(a, s);
+}
+
+cudaError_t launch_depth_score_backward(const KArgs &a, bool dist_bf16, cudaStream_t s) {
+  const long long npts = a.items * a.LP;
+  if (npts == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)min((npts + kThreads - 1) / kThreads, (long long)148 * 64);
+  if (dist_bf16) dfa3d_depth_score_backward_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(a);
+  else dfa3d_depth_score_backward_kernel<float><<<grid, kThreads, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace dfa3d

@@ -1,0 +1,197 @@
+// extern "C" entry points of libdfa3d_b200.so: argument validation, kernel-argument assembly, error
+// reporting.  Declarations and the reference interfaces they replace: include/dfa3d_b200.h.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/dfa3d_b200.h"
+#include "dfa3d_common.cuh"
+#include "dfa3d_launch.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Checks the descriptor; `need_value` / `need_dist` say which tensors the call reads.
+int check_problem(const dfa3d_problem *p, bool need_value, bool need_dist) {
+  if (!p) return fail(DFA3D_ERR_INVALID_ARGUMENT, "problem descriptor is null");
+  if (p->B < 0 || p->Q < 0) return fail(DFA3D_ERR_INVALID_ARGUMENT, "B and Q must be >= 0");
+  if (p->N <= 0 || p->H <= 0 || p->L <= 0 || p->P <= 0)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "N, H, L, P must be positive (got %d %d %d %d)", p->N,
+                p->H, p->L, p->P);
+  if (p->L > DFA3D_MAX_LEVELS)
+    return fail(DFA3D_ERR_UNSUPPORTED, "L=%d exceeds DFA3D_MAX_LEVELS=%d", p->L, DFA3D_MAX_LEVELS);
+  if ((long long)p->L * p->P > (1 << 20))
+    return fail(DFA3D_ERR_UNSUPPORTED, "L*P=%lld is too large", (long long)p->L * p->P);
+  if (need_value) {
+    if (p->C <= 0 || p->C > DFA3D_MAX_CHANNELS)
+      return fail(DFA3D_ERR_UNSUPPORTED, "C=%d outside [1, %d]", p->C, DFA3D_MAX_CHANNELS);
+    if (p->value_dtype != DFA3D_DTYPE_F32 && p->value_dtype != DFA3D_DTYPE_BF16)
+      return fail(DFA3D_ERR_INVALID_ARGUMENT, "value_dtype %d is not a DFA3D_DTYPE_*", p->value_dtype);
+    if ((long long)p->N * p->H * p->C >= (1LL << 31))
+      return fail(DFA3D_ERR_UNSUPPORTED, "N*H*C must stay below 2^31 (one camera's value slice)");
+  }
+  if (need_dist) {
+    if (p->D <= 0) return fail(DFA3D_ERR_INVALID_ARGUMENT, "D must be positive (got %d)", p->D);
+    if (p->dist_dtype != DFA3D_DTYPE_F32 && p->dist_dtype != DFA3D_DTYPE_BF16)
+      return fail(DFA3D_ERR_INVALID_ARGUMENT, "dist_dtype %d is not a DFA3D_DTYPE_*", p->dist_dtype);
+    if (p->dist_head_stride != 0 && p->dist_head_stride != p->D)
+      return fail(DFA3D_ERR_INVALID_ARGUMENT, "dist_head_stride must be 0 (shared) or D (per head), got %lld",
+                  (long long)p->dist_head_stride);
+    if ((long long)p->N * p->H * p->D >= (1LL << 31))
+      return fail(DFA3D_ERR_UNSUPPORTED, "N*H*D must stay below 2^31 (one camera's dist slice)");
+  }
+  return DFA3D_OK;
+}
+
+#define REQUIRE_PTR(ptr)                                                                 \
+  do {                                                                                    \
+    if (!(ptr)) return fail(DFA3D_ERR_INVALID_ARGUMENT, "argument `%s` is null", #ptr);   \
+  } while (0)
+#define REQUIRE_ALIGNED(ptr)                                                                          \
+  do {                                                                                                 \
+    if (!aligned16(ptr)) return fail(DFA3D_ERR_INVALID_ARGUMENT, "`%s` must be 16-byte aligned", #ptr); \
+  } while (0)
+
+dfa3d::KArgs base_args(const dfa3d_problem *p, int shape_stride, int loc_stride) {
+  dfa3d::KArgs a;
+  memset(&a, 0, sizeof(a));
+  a.B = p->B; a.N = p->N; a.H = p->H; a.C = p->C; a.D = p->D; a.L = p->L; a.Q = p->Q; a.P = p->P;
+  a.LP = p->L * p->P;
+  a.shape_stride = shape_stride;
+  a.loc_stride = loc_stride;
+  a.items = (long long)p->B * p->Q * p->H;
+  a.dist_head_stride = p->dist_head_stride;
+  a.dist_pix_stride = p->dist_head_stride == 0 ? (long long)p->D : (long long)p->H * p->D;
+  return a;
+}
+
+int finish(cudaError_t e, const char *what) {
+  if (e != cudaSuccess)
+    return fail(DFA3D_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return DFA3D_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dfa3d_abi_version(void) { return DFA3D_ABI_VERSION; }
+
+const char *dfa3d_last_error(void) { return g_err; }
+
+int dfa3d_depth_score_forward(const dfa3d_problem *p, const void *dist, const int64_t *shapes3,
+                              const int64_t *level_start, const float *loc3, float *depth_score,
+                              void *stream) {
+  if (int rc = check_problem(p, false, true)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start); REQUIRE_PTR(loc3);
+  REQUIRE_PTR(depth_score); REQUIRE_ALIGNED(depth_score);
+  dfa3d::KArgs a = base_args(p, 3, 3);
+  a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3; a.ds_out = depth_score;
+  return finish(dfa3d::launch_depth_score_forward(a, p->dist_dtype == DFA3D_DTYPE_BF16,
+                                                  (cudaStream_t)stream),
+                "dfa3d_depth_score_forward launch");
+}
+
+int dfa3d_depth_score_backward(const dfa3d_problem *p, const void *dist, const int64_t *shapes3,
+                               const int64_t *level_start, const float *loc3,
+                               const float *grad_depth_score, float *grad_dist, float *grad_loc3,
+                               void *stream) {
+  if (int rc = check_problem(p, false, true)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start); REQUIRE_PTR(loc3);
+  REQUIRE_PTR(grad_depth_score); REQUIRE_PTR(grad_dist); REQUIRE_PTR(grad_loc3);
+  REQUIRE_ALIGNED(grad_depth_score);
+  dfa3d::KArgs a = base_args(p, 3, 3);
+  a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
+  a.grad_ds_in = grad_depth_score; a.grad_dist = grad_dist; a.grad_loc = grad_loc3;
+  return finish(dfa3d::launch_depth_score_backward(a, p->dist_dtype == DFA3D_DTYPE_BF16,
+                                                   (cudaStream_t)stream),
+                "dfa3d_depth_score_backward launch");
+}
+
+int dfa3d_wms_attn_forward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
+                           const int64_t *level_start, const float *loc2, const float *attn,
+                           const float *depth_score, float *out, void *stream) {
+  if (int rc = check_problem(p, true, false)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(shapes2); REQUIRE_PTR(level_start); REQUIRE_PTR(loc2);
+  REQUIRE_PTR(attn); REQUIRE_PTR(depth_score); REQUIRE_PTR(out);
+  REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(depth_score); REQUIRE_ALIGNED(out);
+  dfa3d::KArgs a = base_args(p, 2, 2);
+  a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn;
+  a.ds_in = depth_score; a.out = out;
+  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16, false, true,
+                                      (cudaStream_t)stream),
+                "dfa3d_wms_attn_forward launch");
+}
+
+int dfa3d_wms_attn_backward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
+                            const int64_t *level_start, const float *loc2, const float *attn,
+                            const float *depth_score, const float *grad_out, float *grad_value,
+                            float *grad_loc2, float *grad_attn, float *grad_depth_score,
+                            void *stream) {
+  if (int rc = check_problem(p, true, false)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(shapes2); REQUIRE_PTR(level_start); REQUIRE_PTR(loc2);
+  REQUIRE_PTR(attn); REQUIRE_PTR(depth_score); REQUIRE_PTR(grad_out); REQUIRE_PTR(grad_value);
+  REQUIRE_PTR(grad_loc2); REQUIRE_PTR(grad_attn); REQUIRE_PTR(grad_depth_score);
+  REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(depth_score); REQUIRE_ALIGNED(grad_out);
+  REQUIRE_ALIGNED(grad_value); REQUIRE_ALIGNED(grad_depth_score);
+  dfa3d::KArgs a = base_args(p, 2, 2);
+  a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn;
+  a.ds_in = depth_score; a.grad_out = grad_out; a.grad_value = grad_value; a.grad_loc = grad_loc2;
+  a.grad_attn = grad_attn; a.grad_ds_out = grad_depth_score;
+  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16, false, true,
+                                       (cudaStream_t)stream),
+                "dfa3d_wms_attn_backward launch");
+}
+
+int dfa3d_fused_forward(const dfa3d_problem *p, const void *value, const void *dist,
+                        const int64_t *shapes3, const int64_t *level_start, const float *loc3,
+                        const float *attn, float *out, float *depth_score_out, void *stream) {
+  if (int rc = check_problem(p, true, true)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start);
+  REQUIRE_PTR(loc3); REQUIRE_PTR(attn); REQUIRE_PTR(out);
+  REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(out); REQUIRE_ALIGNED(depth_score_out);
+  dfa3d::KArgs a = base_args(p, 3, 3);
+  a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
+  a.attn = attn; a.out = out; a.ds_out = depth_score_out;
+  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16,
+                                      p->dist_dtype == DFA3D_DTYPE_BF16, false, (cudaStream_t)stream),
+                "dfa3d_fused_forward launch");
+}
+
+int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *dist,
+                         const int64_t *shapes3, const int64_t *level_start, const float *loc3,
+                         const float *attn, const float *grad_out, float *grad_value,
+                         float *grad_dist, float *grad_loc3, float *grad_attn, void *stream) {
+  if (int rc = check_problem(p, true, true)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start);
+  REQUIRE_PTR(loc3); REQUIRE_PTR(attn); REQUIRE_PTR(grad_out); REQUIRE_PTR(grad_value);
+  REQUIRE_PTR(grad_dist); REQUIRE_PTR(grad_loc3); REQUIRE_PTR(grad_attn);
+  REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(grad_out); REQUIRE_ALIGNED(grad_value);
+  dfa3d::KArgs a = base_args(p, 3, 3);
+  a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
+  a.attn = attn; a.grad_out = grad_out; a.grad_value = grad_value; a.grad_dist = grad_dist;
+  a.grad_loc = grad_loc3; a.grad_attn = grad_attn;
+  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16,
+                                       p->dist_dtype == DFA3D_DTYPE_BF16, false, (cudaStream_t)stream),
+                "dfa3d_fused_backward launch");
+}
+
+}  // extern "C"

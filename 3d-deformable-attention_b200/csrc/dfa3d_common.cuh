@@ -1,0 +1,163 @@
+// Shared device helpers of the DFA3D kernels (sm_100a).
+//
+// Geometry conventions are the reference's
+// (DFA3D/dfa3D/ops/csrc/common/cuda/ms_depth_score_sample_cuda_kernel.cuh:128-141 and
+//  wms_deform_attn_cuda_kernel.cuh:280-294):
+//   pixel coordinate  = fma(loc, size, -0.5)  -- ONE rounding.  The reference writes `loc * size - 0.5`
+//                       and nvcc's default contraction turns it into a fused multiply-add; with a
+//                       separately rounded product about 1e-5 of the points of a BEVFormer-base
+//                       sized problem fall into the neighbouring cell, which changes the
+//                       (discontinuous) depth_score slots and location gradients against the
+//                       reference op.  With fmaf none were observed to.
+//   2-D range test    = h > -1 && w > -1 && h < H && w < W          (strict)
+//   3-D range test    = 2-D test && d > -1 && d < D
+//   corner k          : 0=(y0,x0) 1=(y0,x1) 2=(y1,x1) 3=(y1,x0);  in-image iff 0 <= y <= H-1, 0 <= x <= W-1
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dfa3d {
+
+constexpr int kMaxLevels = 32;
+constexpr int kWarpsPerCta = 8;
+constexpr int kThreads = kWarpsPerCta * 32;
+
+// Kernel argument block (device pointers + sizes).  Unused pointers are null.
+struct KArgs {
+  const void *value;       // (B,N,H,C) fp32|bf16
+  const void *dist;        // (B,N,H,D) or (B,N,D) fp32|bf16
+  const int64_t *shapes;   // (L, shape_stride) int64
+  const int64_t *lsi;      // (L) int64
+  const float *loc;        // (B,Q,H,L,P,loc_stride)
+  const float *attn;       // (B,Q,H,L,P)
+  const float *ds_in;      // (B,Q,H,L,P,4) given depth score (two-stage attention)
+  const float *grad_out;   // (B,Q,H*C)
+  const float *grad_ds_in; // (B,Q,H,L,P,4) incoming depth-score gradient (two-stage depth backward)
+  float *out;              // (B,Q,H*C)
+  float *ds_out;           // (B,Q,H,L,P,4) or null
+  float *grad_value;       // (B,N,H,C) fp32, accumulated
+  float *grad_dist;        // layout of dist, fp32, accumulated
+  float *grad_loc;         // (B,Q,H,L,P,loc_stride), overwritten
+  float *grad_attn;        // (B,Q,H,L,P), overwritten
+  float *grad_ds_out;      // (B,Q,H,L,P,4), overwritten, or null
+  int B, N, H, C, D, L, Q, P;
+  int LP;                  // L*P
+  int shape_stride;        // 2 or 3
+  int loc_stride;          // 2 or 3
+  long long items;         // B*Q*H
+  long long dist_pix_stride;   // elements between pixels of dist: H*D or D
+  long long dist_head_stride;  // D or 0
+};
+
+// Level table staged in shared memory once per CTA.
+struct LevelTable {
+  int h[kMaxLevels], w[kMaxLevels], d[kMaxLevels], start[kMaxLevels];
+};
+
+__device__ __forceinline__ void stage_levels(LevelTable &t, const KArgs &a) {
+  for (int l = threadIdx.x; l < a.L; l += blockDim.x) {
+    t.h[l] = (int)a.shapes[l * a.shape_stride];
+    t.w[l] = (int)a.shapes[l * a.shape_stride + 1];
+    t.d[l] = a.shape_stride == 3 ? (int)a.shapes[l * 3 + 2] : a.D;
+    t.start[l] = (int)a.lsi[l];
+  }
+  __syncthreads();
+}
+
+// Geometry of one sampling point.
+struct PointGeo {
+  float lw, lh, ld;   // fractional parts; hw = 1-lw etc.
+  int pix[4];         // pixel index inside the camera (level start included), -1 if corner k unusable
+  int z0;             // lower depth bin (may be -1); upper = z0+1
+  int W, Hh, Dd;
+  bool ok2, ok3;
+};
+
+// `has_z`: the location carries a depth coordinate (3-D range test applies to ok3).
+// Corner pixels are additionally bounded by N so that inconsistent shape tables cannot make the
+// kernels touch memory outside the tensors (such corners are treated as outside the image).
+__device__ __forceinline__ PointGeo point_geometry(float x, float y, float z, bool has_z, int Hh,
+                                                   int W, int Dd, int start, int N) {
+  PointGeo g;
+  g.W = W; g.Hh = Hh; g.Dd = Dd;
+  const float w_im = fmaf(x, (float)W, -0.5f);
+  const float h_im = fmaf(y, (float)Hh, -0.5f);
+  g.ok2 = (h_im > -1.f) && (w_im > -1.f) && (h_im < (float)Hh) && (w_im < (float)W);
+  float d_im = 0.f;
+  g.ok3 = false;
+  if (has_z) {
+    d_im = fmaf(z, (float)Dd, -0.5f);
+    g.ok3 = g.ok2 && (d_im > -1.f) && (d_im < (float)Dd);
+  }
+  const float wf = floorf(w_im), hf = floorf(h_im), df = floorf(d_im);
+  const int x0 = g.ok2 ? (int)wf : 0, y0 = g.ok2 ? (int)hf : 0;
+  g.lw = w_im - wf; g.lh = h_im - hf; g.ld = d_im - df;
+  g.z0 = g.ok3 ? (int)df : 0;
+  const int x1 = x0 + 1, y1 = y0 + 1;
+  const bool xl = x0 >= 0, xh = x1 <= W - 1, yl = y0 >= 0, yh = y1 <= Hh - 1;
+  const int base = start + y0 * W + x0;
+  const int p0 = base, p1 = base + 1, p2 = base + W + 1, p3 = base + W;
+  g.pix[0] = (g.ok2 && yl && xl && p0 < N) ? p0 : -1;
+  g.pix[1] = (g.ok2 && yl && xh && p1 < N) ? p1 : -1;
+  g.pix[2] = (g.ok2 && yh && xh && p2 < N) ? p2 : -1;
+  g.pix[3] = (g.ok2 && yh && xl && p3 < N) ? p3 : -1;
+  return g;
+}
+
+__device__ __forceinline__ void bilinear_weights(const PointGeo &g, float bw[4]) {
+  const float hw = 1.f - g.lw, hh = 1.f - g.lh;
+  bw[0] = hh * hw; bw[1] = hh * g.lw; bw[2] = g.lh * g.lw; bw[3] = g.lh * hw;
+}
+
+__device__ __forceinline__ float load_scalar(const float *p) { return __ldg(p); }
+__device__ __forceinline__ float load_scalar(const __nv_bfloat16 *p) {
+  return __bfloat162float(__ldg(p));
+}
+
+// The two depth bins of corner k (0 where the bin is outside [0, D-1] or the corner is unusable).
+template <typename DT>
+__device__ __forceinline__ void load_depth_pair(const DT *dist_bh, long long pix_stride, int pix,
+                                                int z0, int Dd, int Dchan, bool ok3, float &lo,
+                                                float &hi) {
+  lo = 0.f; hi = 0.f;
+  if (ok3 && pix >= 0) {
+    const DT *p = dist_bh + (long long)pix * pix_stride;
+    if (z0 >= 0 && z0 < Dchan) lo = load_scalar(p + z0);
+    if (z0 + 1 <= Dd - 1 && z0 + 1 < Dchan) hi = load_scalar(p + z0 + 1);
+  }
+}
+
+// 16-byte read-only load of a value-row fragment, widened to fp32.
+template <typename VT> struct RowVec;
+template <> struct RowVec<float> {
+  static constexpr int kElems = 4;
+  __device__ static __forceinline__ void load(const float *p, float (&v)[4]) {
+    const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+};
+template <> struct RowVec<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  __device__ static __forceinline__ void load(const __nv_bfloat16 *p, float (&v)[8]) {
+    const uint4 t = __ldg(reinterpret_cast<const uint4 *>(p));
+    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {           // bf16 -> fp32 is a 16-bit shift
+      v[2 * i] = __uint_as_float(u[i] << 16);
+      v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+  }
+};
+
+// Vectorised fire-and-forget fp32 reduction into global memory (one 16-byte L2 atomic, sm_90+).
+__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void red_add(float *addr, float a) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
+}
+
+}  // namespace dfa3d

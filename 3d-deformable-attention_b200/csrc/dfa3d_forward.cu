@@ -1,0 +1,286 @@
+// DFA3D forward kernels (sm_100a).
+//
+// One warp owns one (camera b, query q, head h) item.  The L*P sampling points of the item are taken
+// 32 at a time:
+//   prologue  -- lane j owns point j: it reads its location and attention weight (coalesced), derives
+//                the four bilinear corners, and (fused mode) gathers the 8 depth-distribution values
+//                that give the four per-corner depth scores; it leaves one {row offset, weight} pair
+//                per corner in the warp's slice of shared memory;
+//   gather    -- the warp walks the (point, corner) rows; a group of G lanes reads one value row with
+//                16-byte loads, so one warp-wide request fetches 32/G rows, and every lane
+//                accumulates weight * row fragment;
+//   epilogue  -- the 32/G partial sums are folded with xor-shuffles and G lanes store the output row.
+// This replaces the reference's pair of kernels (one thread per (b,q,h) for the depth scores,
+// ms_depth_score_sample_cuda_kernel.cuh:94-148; one thread per output channel for the attention,
+// wms_deform_attn_cuda_kernel.cuh:240-303) and the depth_score round trip through HBM between them.
+#include "dfa3d_common.cuh"
+#include "dfa3d_launch.h"
+
+namespace dfa3d {
+
+enum FwdMode { kFused = 0, kGivenDepthScore = 1 };
+
+struct __align__(8) RowEntry {
+  int off;    // element offset of the row inside the (b, h) slice of value; -1 = skip
+  float wgt;  // attention * bilinear * depth score
+};
+
+// ------------------------------------------------------------------------------------------------
+// prologue shared by forward and backward: per-lane point -> 4 row entries (+ depth scores)
+// ------------------------------------------------------------------------------------------------
+template <typename DT, int MODE>
+__device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, long long item, int j,
+                                          int b, int h, float (&ds)[4], float (&wgt)[4],
+                                          int (&off)[4]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { ds[k] = 0.f; wgt[k] = 0.f; off[k] = -1; }
+  if (j >= a.LP) return;
+  const int l = j / a.P;
+  const long long pt = item * a.LP + j;
+  const float *lp = a.loc + pt * a.loc_stride;
+  const float x = __ldg(lp), y = __ldg(lp + 1);
+  const float z = (MODE == kFused) ? __ldg(lp + 2) : 0.f;
+  const float aw = __ldg(a.attn + pt);
+  const PointGeo g = point_geometry(x, y, z, MODE == kFused, lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N);
+  if (!g.ok2) return;
+  float bw[4];
+  bilinear_weights(g, bw);
+  if (MODE == kFused) {
+    const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
+                        (long long)b * a.N * a.dist_pix_stride + (long long)h * a.dist_head_stride;
+    float lo[4], hi[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, g.Dd, a.D, g.ok3, lo[k], hi[k]);
+    const float hd = 1.f - g.ld;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) ds[k] = g.ok3 ? lo[k] * hd + hi[k] * g.ld : 0.f;
+  } else {
+    const float4 t = __ldg(reinterpret_cast<const float4 *>(a.ds_in) + pt);
+    ds[0] = g.pix[0] >= 0 ? t.x : 0.f;
+    ds[1] = g.pix[1] >= 0 ? t.y : 0.f;
+    ds[2] = g.pix[2] >= 0 ? t.z : 0.f;
+    ds[3] = g.pix[3] >= 0 ? t.w : 0.f;
+  }
+  const int row = a.H * a.C;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (g.pix[k] >= 0) {
+      off[k] = g.pix[k] * row;
+      wgt[k] = aw * (bw[k] * ds[k]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// fused / given-depth-score forward, C a power of two with 16-byte row fragments
+// ------------------------------------------------------------------------------------------------
+template <typename VT, typename DT, int C, int MODE, bool WRITE_DS>
+__global__ void __launch_bounds__(kThreads)
+dfa3d_forward_kernel(const KArgs a) {
+  constexpr int V = RowVec<VT>::kElems;   // elements per 16-byte fragment
+  constexpr int G = C / V;                // lanes per row
+  constexpr int R = 32 / G;               // rows per warp-wide request
+  constexpr int U = 4;                    // requests in flight per lane
+  static_assert(G >= 1 && G <= 32 && (G & (G - 1)) == 0, "C/V must be a power of two <= 32");
+
+  __shared__ LevelTable lv;
+  __shared__ RowEntry rows[kWarpsPerCta][128];
+  stage_levels(lv, a);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * kWarpsPerCta + warp;
+  if (item >= a.items) return;
+  const int h = (int)(item % a.H);
+  const int b = (int)(item / ((long long)a.Q * a.H));
+  const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)b * a.N * a.H + h) * C +
+                    (lane % G) * V;
+  const int grp = lane / G;
+  RowEntry *my = rows[warp];
+
+  float acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = 0.f;
+
+  for (int chunk = 0; chunk < a.LP; chunk += 32) {
+    float ds[4], wgt[4];
+    int off[4];
+    fwd_point<DT, MODE>(a, lv, item, chunk + lane, b, h, ds, wgt, off);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) my[lane * 4 + k] = RowEntry{off[k], wgt[k]};
+    if (WRITE_DS && chunk + lane < a.LP)
+      reinterpret_cast<float4 *>(a.ds_out)[item * a.LP + chunk + lane] =
+          make_float4(ds[0], ds[1], ds[2], ds[3]);
+    __syncwarp();
+    const int nrows = min(32, a.LP - chunk) * 4;
+    for (int r0 = 0; r0 < nrows; r0 += R * U) {
+      RowEntry e[U];
+      float v[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int r = r0 + u * R + grp;
+        e[u] = (r < nrows) ? my[r] : RowEntry{-1, 0.f};
+        if (e[u].wgt == 0.f) e[u].off = -1;   // nothing to add: skip the fetch
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (e[u].off >= 0) {
+          RowVec<VT>::load(vbase + e[u].off, v[u]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) v[u][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(e[u].wgt, v[u][i], acc[i]);
+    }
+    __syncwarp();
+  }
+#pragma unroll
+  for (int s = G; s < 32; s <<= 1)
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], s);
+  if (lane < G) {
+    float *o = a.out + item * C + lane * V;
+#pragma unroll
+    for (int i = 0; i < V; i += 4)
+      *reinterpret_cast<float4 *>(o + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// any C: lanes stride over channels, rows walked one by one (correctness path for unusual widths)
+// ------------------------------------------------------------------------------------------------
+template <typename VT, typename DT, int MODE, bool WRITE_DS>
+__global__ void __launch_bounds__(kThreads)
+dfa3d_forward_generic_kernel(const KArgs a) {
+  __shared__ LevelTable lv;
+  __shared__ RowEntry rows[kWarpsPerCta][128];
+  stage_levels(lv, a);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * kWarpsPerCta + warp;
+  if (item >= a.items) return;
+  const int C = a.C;
+  const int h = (int)(item % a.H);
+  const int b = (int)(item / ((long long)a.Q * a.H));
+  const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)b * a.N * a.H + h) * C;
+  RowEntry *my = rows[warp];
+  for (int c0 = 0; c0 < C; c0 += 32) {          // C <= 1024: at most 32 passes
+    const int c = c0 + lane;
+    float acc = 0.f;
+    for (int chunk = 0; chunk < a.LP; chunk += 32) {
+      float ds[4], wgt[4];
+      int off[4];
+      fwd_point<DT, MODE>(a, lv, item, chunk + lane, b, h, ds, wgt, off);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) my[lane * 4 + k] = RowEntry{off[k], wgt[k]};
+      if (WRITE_DS && c0 == 0 && chunk + lane < a.LP)
+        reinterpret_cast<float4 *>(a.ds_out)[item * a.LP + chunk + lane] =
+            make_float4(ds[0], ds[1], ds[2], ds[3]);
+      __syncwarp();
+      const int nrows = min(32, a.LP - chunk) * 4;
+      if (c < C)
+        for (int r = 0; r < nrows; ++r) {
+          const RowEntry e = my[r];
+          if (e.off >= 0 && e.wgt != 0.f) acc = fmaf(e.wgt, load_scalar(vbase + e.off + c), acc);
+        }
+      __syncwarp();
+    }
+    if (c < C) a.out[item * C + c] = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// depth scores only (two-stage API): one thread per sampling point
+// ------------------------------------------------------------------------------------------------
+template <typename DT>
+__global__ void __launch_bounds__(kThreads)
+dfa3d_depth_score_forward_kernel(const KArgs a) {
+  __shared__ LevelTable lv;
+  stage_levels(lv, a);
+  const long long npts = a.items * a.LP;
+  for (long long pt = (long long)blockIdx.x * blockDim.x + threadIdx.x; pt < npts;
+       pt += (long long)gridDim.x * blockDim.x) {
+    const long long item = pt / a.LP;
+    const int j = (int)(pt - item * a.LP);
+    const int l = j / a.P;
+    const int h = (int)(item % a.H);
+    const int b = (int)(item / ((long long)a.Q * a.H));
+    const float *lp = a.loc + pt * 3;
+    const PointGeo g = point_geometry(__ldg(lp), __ldg(lp + 1), __ldg(lp + 2), true, lv.h[l], lv.w[l],
+                                      lv.d[l], lv.start[l], a.N);
+    const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
+                        (long long)b * a.N * a.dist_pix_stride + (long long)h * a.dist_head_stride;
+    float ds[4];
+    const float hd = 1.f - g.ld;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float lo, hi;
+      load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, g.Dd, a.D, g.ok3, lo, hi);
+      ds[k] = g.ok3 ? lo * hd + hi * g.ld : 0.f;
+    }
+    reinterpret_cast<float4 *>(a.ds_out)[pt] = make_float4(ds[0], ds[1], ds[2], ds[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side dispatch
+// ------------------------------------------------------------------------------------------------
+template <typename VT, typename DT, int MODE, bool WRITE_DS>
+static cudaError_t launch_forward_c(const KArgs &a, cudaStream_t s) {
+  const unsigned grid = (unsigned)((a.items + kWarpsPerCta - 1) / kWarpsPerCta);
+  constexpr int V = RowVec<VT>::kElems;
+  switch (a.C / V) {
+    case 2:  dfa3d_forward_kernel<VT, DT, 2 * V, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
+    case 4:  dfa3d_forward_kernel<VT, DT, 4 * V, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
+    case 8:  dfa3d_forward_kernel<VT, DT, 8 * V, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
+    case 16: dfa3d_forward_kernel<VT, DT, 16 * V, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
+    default: dfa3d_forward_generic_kernel<VT, DT, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
+  }
+  return cudaGetLastError();
+}
+
+static bool vector_path_ok(const KArgs &a, int V) {
+  const int g = a.C / V;
+  return a.C % V == 0 && (g == 2 || g == 4 || g == 8 || g == 16);
+}
+
+template <typename VT, typename DT, int MODE>
+static cudaError_t launch_forward_vd(const KArgs &a, cudaStream_t s) {
+  const bool gen = !vector_path_ok(a, RowVec<VT>::kElems);
+  const unsigned grid = (unsigned)((a.items + kWarpsPerCta - 1) / kWarpsPerCta);
+  if (gen) {
+    if (a.ds_out) dfa3d_forward_generic_kernel<VT, DT, MODE, true><<<grid, kThreads, 0, s>>>(a);
+    else dfa3d_forward_generic_kernel<VT, DT, MODE, false><<<grid, kThreads, 0, s>>>(a);
+    return cudaGetLastError();
+  }
+  return a.ds_out ? launch_forward_c<VT, DT, MODE, true>(a, s)
+                  : launch_forward_c<VT, DT, MODE, false>(a, s);
+}
+
+cudaError_t launch_forward(const KArgs &a, bool value_bf16, bool dist_bf16, bool given_ds,
+                           cudaStream_t s) {
+  if (a.items == 0) return cudaSuccess;
+  if (given_ds) {   // dist is not read: its type parameter is irrelevant
+    return value_bf16 ? launch_forward_vd<__nv_bfloat16, float, kGivenDepthScore>(a, s)
+                      : launch_forward_vd<float, float, kGivenDepthScore>(a, s);
+  }
+  if (value_bf16)
+    return dist_bf16 ? launch_forward_vd<__nv_bfloat16, __nv_bfloat16, kFused>(a, s)
+                     : launch_forward_vd<__nv_bfloat16, float, kFused>(a, s);
+  return dist_bf16 ? launch_forward_vd<float, __nv_bfloat16, kFused>(a, s)
+                   : launch_forward_vd<float, float, kFused>(a, s);
+}
+
+cudaError_t launch_depth_score_forward(const KArgs &a, bool dist_bf16, cudaStream_t s) {
+  const long long npts = a.items * a.LP;
+  if (npts == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)min((npts + kThreads - 1) / kThreads, (long long)148 * 64);
+  if (dist_bf16) dfa3d_depth_score_forward_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(a);
+  else dfa3d_depth_score_forward_kernel<float><<<grid, kThreads, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace dfa3d

@@ -1,0 +1,24 @@
+"""dfa3d_b200 -- B200 (sm_100a) implementation of the DFA3D operator behind the reference's API.
+
+The compute lives in ``libdfa3d_b200.so`` (hand-written CUDA behind a C ABI, include/dfa3d_b200.h);
+this package is the PyTorch-facing host side: ``ext`` mirrors the reference's extension module,
+``functions`` its autograd Functions.  There is no fallback path: without the shared library the
+operators raise.
+"""
+from . import _lib, ext  # noqa: F401
+from .functions import (  # noqa: F401
+    MultiScale3DDeformableAttnFunction,
+    MultiScale3DDeformableAttnFunction_fp32,
+    MultiScaleDepthScoreSampleFunction,
+    MultiScaleDepthScoreSampleFunction_fp32,
+    WeightedMultiScaleDeformableAttnFunction,
+    WeightedMultiScaleDeformableAttnFunction_fp32,
+)
+
+__all__ = [
+    "ext",
+    "MultiScaleDepthScoreSampleFunction", "WeightedMultiScaleDeformableAttnFunction",
+    "MultiScale3DDeformableAttnFunction",
+    "MultiScaleDepthScoreSampleFunction_fp32", "WeightedMultiScaleDeformableAttnFunction_fp32",
+    "MultiScale3DDeformableAttnFunction_fp32",
+]

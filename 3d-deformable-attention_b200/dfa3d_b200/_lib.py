@@ -1,0 +1,75 @@
+"""ctypes binding of libdfa3d_b200.so (the C ABI declared in include/dfa3d_b200.h).
+
+There is no CPU or pure-PyTorch fallback: if the shared library is missing or a call fails, an
+exception is raised.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("DFA3D_B200_LIB") or os.path.join(_HERE, "libdfa3d_b200.so")
+
+ABI_VERSION = 1
+DTYPE_F32 = 0
+DTYPE_BF16 = 1
+MAX_LEVELS = 32
+MAX_CHANNELS = 1024
+
+ERROR_NAMES = {-1: "invalid argument", -2: "unsupported", -3: "CUDA error"}
+
+
+class Problem(ctypes.Structure):
+    """struct dfa3d_problem."""
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ("B", "N", "H", "C", "D", "L", "Q", "P", "value_dtype", "dist_dtype")] + \
+               [("dist_head_stride", ctypes.c_int64)]
+
+
+_P = ctypes.POINTER(Problem)
+_V = ctypes.c_void_p
+
+# name -> number of pointer arguments after the problem descriptor (the stream included)
+ENTRY_POINTS = {
+    "dfa3d_depth_score_forward": 6,
+    "dfa3d_depth_score_backward": 8,
+    "dfa3d_wms_attn_forward": 8,
+    "dfa3d_wms_attn_backward": 12,
+    "dfa3d_fused_forward": 9,
+    "dfa3d_fused_backward": 12,
+}
+
+_lib = None
+
+
+def load():
+    """Load the library once; raise with build instructions if it is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `python 3d-deformable-attention_b200/build.py` "
+            "(needs nvcc; targets sm_100a). dfa3d_b200 has no fallback implementation.")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.dfa3d_abi_version.restype = ctypes.c_int
+    lib.dfa3d_abi_version.argtypes = []
+    lib.dfa3d_last_error.restype = ctypes.c_char_p
+    lib.dfa3d_last_error.argtypes = []
+    for name, nptr in ENTRY_POINTS.items():
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [_P] + [_V] * nptr
+    got = lib.dfa3d_abi_version()
+    if got != ABI_VERSION:
+        raise ImportError(f"libdfa3d_b200.so has ABI version {got}, this package expects {ABI_VERSION}")
+    _lib = lib
+    return lib
+
+
+def call(name, problem, *ptrs):
+    """Invoke an entry point; raise RuntimeError carrying dfa3d_last_error() on failure."""
+    lib = load()
+    rc = getattr(lib, name)(ctypes.byref(problem), *ptrs)
+    if rc != 0:
+        msg = lib.dfa3d_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{name} failed ({ERROR_NAMES.get(rc, rc)}): {msg}")

@@ -1,0 +1,244 @@
+"""Drop-in for the reference's compiled extension module ``dfa3D._ext``.
+
+The four functions have the names, keyword arguments, return values and in-place conventions of the
+reference's pybind module (DFA3D/dfa3D/ops/csrc/pybind.cpp:42-66); two more expose the one-launch
+fused forward / backward.  All of them validate their tensors like the reference's launchers
+(contiguous, CUDA, ``batch % min(batch, im2col_step) == 0`` -- DFA3D/dfa3D/ops/csrc/cuda/
+wms_deform_attn_cuda.cu:220-253) and then call the C ABI on the current CUDA stream.
+
+Narrowing with respect to the reference: tensors are float32 (the reference also instantiates
+float64), plus bfloat16 storage for ``value`` / ``dist`` which the reference lacks.
+"""
+import torch
+
+from . import _lib
+
+
+def _chk(t, name, dtypes=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} tensor has to be contiguous")
+    if dtypes is not None and t.dtype not in dtypes:
+        raise RuntimeError(f"{name} has dtype {t.dtype}; supported: {dtypes}")
+
+
+def _same_device(*ts):
+    dev = ts[0].device
+    for t in ts[1:]:
+        if t is not None and t.device != dev:
+            raise RuntimeError(f"all tensors must be on one device, got {dev} and {t.device}")
+
+
+def _step_check(batch, im2col_step):
+    # the reference asserts this although only its chunk loop needs it; kept for identical errors
+    if batch > 0:
+        step = min(batch, int(im2col_step))
+        if step <= 0 or batch % step != 0:
+            raise RuntimeError(f"batch({batch}) must divide im2col_step({step})")
+
+
+_F32 = (torch.float32,)
+_VAL = (torch.float32, torch.bfloat16)
+_I64 = (torch.int64,)
+
+
+def _dt(t):
+    return _lib.DTYPE_BF16 if t.dtype == torch.bfloat16 else _lib.DTYPE_F32
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dist_problem(dist, H):
+    """dist is (B,N,H,D), or (B,N,D) shared by all heads.  Returns (B, N, D, head_stride)."""
+    if dist.dim() == 4:
+        B, N, Hd, D = dist.shape
+        if Hd != H:
+            raise RuntimeError(f"dist has {Hd} heads, expected {H}")
+        return B, N, D, D
+    if dist.dim() == 3:
+        B, N, D = dist.shape
+        return B, N, D, 0
+    raise RuntimeError("dist must be (B,N,H,D) or (B,N,D)")
+
+
+def _loc_dims(loc, last):
+    if loc.dim() != 6 or loc.shape[-1] != last:
+        raise RuntimeError(f"sampling_locations must be (B,Q,H,L,P,{last}), got {tuple(loc.shape)}")
+    return loc.shape[:5]
+
+
+# ------------------------------------------------------------------------------------------------
+def ms_depth_score_sample_forward(value, value_spatial_shapes, value_level_start_index,
+                                  sampling_locations, im2col_step):
+    """`value` is the depth distribution (B,N,H,D) [or (B,N,D)]; returns depth_score (B,Q,H,L,P,4)."""
+    dist = value
+    _chk(dist, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    _chk(value_level_start_index, "level_start_index", _I64)
+    _chk(sampling_locations, "sampling_loc", _F32)
+    _same_device(dist, value_spatial_shapes, value_level_start_index, sampling_locations)
+    B, Q, H, L, P = _loc_dims(sampling_locations, 3)
+    Bd, N, D, hs = _dist_problem(dist, H)
+    if Bd != B or tuple(value_spatial_shapes.shape) != (L, 3):
+        raise RuntimeError("inconsistent shapes between value, spatial_shapes (L,3) and sampling_loc")
+    _step_check(B, im2col_step)
+    out = torch.empty((B, Q, H, L, P, 4), dtype=torch.float32, device=dist.device)
+    pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs)
+    with torch.cuda.device(dist.device):
+        _lib.call("dfa3d_depth_score_forward", pr, _ptr(dist), _ptr(value_spatial_shapes),
+                  _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(out), _stream(dist))
+    return out
+
+
+def ms_depth_score_sample_backward(value, value_spatial_shapes, value_level_start_index,
+                                   sampling_locations, grad_output, grad_value, grad_sampling_loc,
+                                   im2col_step):
+    """Accumulates into grad_value (layout of `value`, float32, caller-zeroed) and overwrites
+    grad_sampling_loc (B,Q,H,L,P,3) with (0, 0, dL/dz)."""
+    dist = value
+    _chk(dist, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    _chk(value_level_start_index, "level_start_index", _I64)
+    _chk(sampling_locations, "sampling_loc", _F32); _chk(grad_output, "grad_output", _F32)
+    _chk(grad_value, "grad_value", _F32); _chk(grad_sampling_loc, "grad_sampling_loc", _F32)
+    _same_device(dist, value_spatial_shapes, value_level_start_index, sampling_locations, grad_output,
+                 grad_value, grad_sampling_loc)
+    B, Q, H, L, P = _loc_dims(sampling_locations, 3)
+    Bd, N, D, hs = _dist_problem(dist, H)
+    if grad_value.shape != dist.shape or grad_sampling_loc.shape != sampling_locations.shape \
+            or tuple(grad_output.shape) != (B, Q, H, L, P, 4):
+        raise RuntimeError("gradient tensors do not match their forward tensors")
+    _step_check(B, im2col_step)
+    pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs)
+    with torch.cuda.device(dist.device):
+        _lib.call("dfa3d_depth_score_backward", pr, _ptr(dist), _ptr(value_spatial_shapes),
+                  _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(grad_output),
+                  _ptr(grad_value), _ptr(grad_sampling_loc), _stream(dist))
+
+
+def wms_deform_attn_forward(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                            attention_weights, depth_scores, im2col_step):
+    """Returns output (B,Q,H*C) float32."""
+    _chk(value, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    _chk(value_level_start_index, "level_start_index", _I64)
+    _chk(sampling_locations, "sampling_loc", _F32); _chk(attention_weights, "attn_weight", _F32)
+    _chk(depth_scores, "depth_score", _F32)
+    _same_device(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                 attention_weights, depth_scores)
+    B, N, H, C = value.shape
+    Bq, Q, Hq, L, P = _loc_dims(sampling_locations, 2)
+    if (Bq, Hq) != (B, H) or tuple(value_spatial_shapes.shape) != (L, 2) \
+            or tuple(attention_weights.shape) != (B, Q, H, L, P) \
+            or tuple(depth_scores.shape) != (B, Q, H, L, P, 4):
+        raise RuntimeError("inconsistent shapes between value, spatial_shapes (L,2), sampling_loc, "
+                           "attn_weight and depth_score")
+    _step_check(B, im2col_step)
+    out = torch.empty((B, Q, H * C), dtype=torch.float32, device=value.device)
+    pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_wms_attn_forward", pr, _ptr(value), _ptr(value_spatial_shapes),
+                  _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(attention_weights),
+                  _ptr(depth_scores), _ptr(out), _stream(value))
+    return out
+
+
+def wms_deform_attn_backward(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                             attention_weights, depth_scores, grad_output, grad_value,
+                             grad_sampling_loc, grad_attn_weight, grad_depth_score, im2col_step):
+    """Accumulates into grad_value (float32, caller-zeroed); overwrites the other three."""
+    _chk(value, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    _chk(value_level_start_index, "level_start_index", _I64)
+    _chk(sampling_locations, "sampling_loc", _F32); _chk(attention_weights, "attn_weight", _F32)
+    _chk(depth_scores, "depth_score", _F32); _chk(grad_output, "grad_output", _F32)
+    _chk(grad_value, "grad_value", _F32); _chk(grad_sampling_loc, "grad_sampling_loc", _F32)
+    _chk(grad_attn_weight, "grad_attn_weight", _F32); _chk(grad_depth_score, "grad_depth_score", _F32)
+    _same_device(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                 attention_weights, depth_scores, grad_output, grad_value, grad_sampling_loc,
+                 grad_attn_weight, grad_depth_score)
+    B, N, H, C = value.shape
+    Bq, Q, Hq, L, P = _loc_dims(sampling_locations, 2)
+    if (Bq, Hq) != (B, H) or tuple(value_spatial_shapes.shape) != (L, 2) \
+            or grad_output.numel() != B * Q * H * C or grad_value.shape != value.shape \
+            or grad_sampling_loc.shape != sampling_locations.shape \
+            or grad_attn_weight.shape != attention_weights.shape \
+            or grad_depth_score.shape != depth_scores.shape:
+        raise RuntimeError("inconsistent shapes in wms_deform_attn_backward")
+    _step_check(B, im2col_step)
+    pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_wms_attn_backward", pr, _ptr(value), _ptr(value_spatial_shapes),
+                  _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(attention_weights),
+                  _ptr(depth_scores), _ptr(grad_output), _ptr(grad_value), _ptr(grad_sampling_loc),
+                  _ptr(grad_attn_weight), _ptr(grad_depth_score), _stream(value))
+
+
+# ------------------------------------------------------------------------------------------------
+# one-launch fused entry points (no counterpart in the reference's extension; they serve the
+# one-stage autograd Function)
+# ------------------------------------------------------------------------------------------------
+def _fused_problem(value, dist, shapes3, lsi, loc3, attn):
+    _chk(value, "value", _VAL); _chk(dist, "value_dpt_dist", _VAL)
+    _chk(shapes3, "spatial_shapes", _I64); _chk(lsi, "level_start_index", _I64)
+    _chk(loc3, "sampling_loc", _F32); _chk(attn, "attn_weight", _F32)
+    _same_device(value, dist, shapes3, lsi, loc3, attn)
+    B, N, H, C = value.shape
+    Bq, Q, Hq, L, P = _loc_dims(loc3, 3)
+    Bd, Nd, D, hs = _dist_problem(dist, H)
+    if (Bq, Hq) != (B, H) or (Bd, Nd) != (B, N) or tuple(shapes3.shape) != (L, 3) \
+            or tuple(attn.shape) != (B, Q, H, L, P):
+        raise RuntimeError("inconsistent shapes between value, value_dpt_dist, spatial_shapes (L,3), "
+                           "sampling_loc and attn_weight")
+    return _lib.Problem(B, N, H, C, D, L, Q, P, _dt(value), _dt(dist), hs), (B, Q, H, L, P, C)
+
+
+def dfa3d_fused_forward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                        sampling_locations, attention_weights, im2col_step, need_depth_score=True):
+    """Returns (output (B,Q,H*C), depth_score (B,Q,H,L,P,4) or None)."""
+    pr, (B, Q, H, L, P, C) = _fused_problem(value, value_dpt_dist, value_spatial_shapes,
+                                            value_level_start_index, sampling_locations,
+                                            attention_weights)
+    _step_check(B, im2col_step)
+    dev = value.device
+    out = torch.empty((B, Q, H * C), dtype=torch.float32, device=dev)
+    ds = torch.empty((B, Q, H, L, P, 4), dtype=torch.float32, device=dev) if need_depth_score else None
+    with torch.cuda.device(dev):
+        _lib.call("dfa3d_fused_forward", pr, _ptr(value), _ptr(value_dpt_dist),
+                  _ptr(value_spatial_shapes), _ptr(value_level_start_index),
+                  _ptr(sampling_locations), _ptr(attention_weights), _ptr(out), _ptr(ds),
+                  _stream(value))
+    return out, ds
+
+
+def dfa3d_fused_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                         sampling_locations, attention_weights, grad_output, grad_value,
+                         grad_value_dpt_dist, grad_sampling_loc, grad_attn_weight, im2col_step):
+    """Accumulates into grad_value and grad_value_dpt_dist (float32, caller-zeroed); overwrites
+    grad_sampling_loc (B,Q,H,L,P,3) and grad_attn_weight."""
+    pr, (B, Q, H, L, P, C) = _fused_problem(value, value_dpt_dist, value_spatial_shapes,
+                                            value_level_start_index, sampling_locations,
+                                            attention_weights)
+    for t, n in ((grad_output, "grad_output"), (grad_value, "grad_value"),
+                 (grad_value_dpt_dist, "grad_value_dpt_dist"), (grad_sampling_loc, "grad_sampling_loc"),
+                 (grad_attn_weight, "grad_attn_weight")):
+        _chk(t, n, _F32)
+    _same_device(value, grad_output, grad_value, grad_value_dpt_dist, grad_sampling_loc,
+                 grad_attn_weight)
+    if grad_output.numel() != B * Q * H * C or grad_value.shape != value.shape \
+            or grad_value_dpt_dist.shape != value_dpt_dist.shape \
+            or grad_sampling_loc.shape != sampling_locations.shape \
+            or grad_attn_weight.shape != attention_weights.shape:
+        raise RuntimeError("inconsistent shapes in dfa3d_fused_backward")
+    _step_check(B, im2col_step)
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_fused_backward", pr, _ptr(value), _ptr(value_dpt_dist),
+                  _ptr(value_spatial_shapes), _ptr(value_level_start_index),
+                  _ptr(sampling_locations), _ptr(attention_weights), _ptr(grad_output),
+                  _ptr(grad_value), _ptr(grad_value_dpt_dist), _ptr(grad_sampling_loc),
+                  _ptr(grad_attn_weight), _stream(value))

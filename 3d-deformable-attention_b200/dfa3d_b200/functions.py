@@ -1,0 +1,127 @@
+"""Autograd Functions with the names, argument order and return conventions of the reference.
+
+  * MultiScaleDepthScoreSampleFunction, WeightedMultiScaleDeformableAttnFunction (two-stage API):
+    DFA3D/dfa3D/ops/multi_scale_3D_deform_attn.py:22-66 and :67-145.
+  * MultiScale3DDeformableAttnFunction (one-stage): semantics of the BEVFormer-side copy
+    BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/
+    multi_scale_3ddeformable_attn_function.py:276-352 (forward returns (output, depth_score); backward
+    returns gradients for value, value_dpt_dist, sampling_locations (x, y and z) and
+    attention_weights).  The package-level copy at multi_scale_3D_deform_attn.py:146-221 cannot run
+    its backward (it returns 8 gradients for 7 inputs and drops the x/y location gradient), so the
+    working copy is the one reproduced.
+  * `_fp32` aliases cast inputs to float32 under autocast like the reference's
+    ``custom_fwd(cast_inputs=torch.float32)`` variants.
+
+Differences, all additive: ``value_dpt_dist`` may also be (B,N,D), shared by all heads (the reference
+needs it repeated per head); ``value`` / ``value_dpt_dist`` may be bfloat16; the one-stage Function
+takes an optional trailing ``return_depth_score`` flag; the one-stage backward is a single kernel
+that recomputes the depth scores instead of re-reading them.
+"""
+import torch
+from torch.autograd.function import Function, once_differentiable
+
+from . import ext as ext_module
+
+
+class MultiScaleDepthScoreSampleFunction(Function):
+    @staticmethod
+    def forward(ctx, value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                im2col_step):
+        """value: depth distribution (B,N,H,D); spatial shapes (L,3); locations (B,Q,H,L,P,3).
+        Returns depth_score (B,Q,H,L,P,4)."""
+        ctx.im2col_step = im2col_step
+        output = ext_module.ms_depth_score_sample_forward(
+            value, value_spatial_shapes, value_level_start_index, sampling_locations,
+            im2col_step=ctx.im2col_step)
+        ctx.save_for_backward(value, value_spatial_shapes, value_level_start_index, sampling_locations)
+        return output
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        value, shapes, lsi, loc = ctx.saved_tensors
+        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_sampling_loc = torch.empty_like(loc)     # every element is written by the kernel
+        ext_module.ms_depth_score_sample_backward(
+            value, shapes, lsi, loc, grad_output.contiguous(), grad_value, grad_sampling_loc,
+            im2col_step=ctx.im2col_step)
+        return grad_value, None, None, grad_sampling_loc, None
+
+
+class WeightedMultiScaleDeformableAttnFunction(Function):
+    @staticmethod
+    def forward(ctx, value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                attention_weights, depth_score, im2col_step):
+        """value (B,N,H,C); spatial shapes (L,2); locations (B,Q,H,L,P,2); attention (B,Q,H,L,P);
+        depth_score (B,Q,H,L,P,4).  Returns (B,Q,H*C)."""
+        ctx.im2col_step = im2col_step
+        output = ext_module.wms_deform_attn_forward(
+            value, value_spatial_shapes, value_level_start_index, sampling_locations,
+            attention_weights, depth_score, im2col_step=ctx.im2col_step)
+        ctx.save_for_backward(value, value_spatial_shapes, value_level_start_index,
+                              sampling_locations, attention_weights, depth_score)
+        return output
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        value, shapes, lsi, loc, attn, depth_score = ctx.saved_tensors
+        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_sampling_loc = torch.empty_like(loc)
+        grad_attn_weight = torch.empty_like(attn)
+        grad_depth_score = torch.empty_like(depth_score)
+        ext_module.wms_deform_attn_backward(
+            value, shapes, lsi, loc, attn, depth_score, grad_output.contiguous(), grad_value,
+            grad_sampling_loc, grad_attn_weight, grad_depth_score, im2col_step=ctx.im2col_step)
+        return grad_value, None, None, grad_sampling_loc, grad_attn_weight, grad_depth_score, None
+
+
+class MultiScale3DDeformableAttnFunction(Function):
+    @staticmethod
+    def forward(ctx, value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                sampling_locations, attention_weights, im2col_step, return_depth_score=True):
+        """value (B,N,H,C); value_dpt_dist (B,N,H,D) or (B,N,D); spatial shapes (L,3);
+        locations (B,Q,H,L,P,3); attention (B,Q,H,L,P).  Returns (output (B,Q,H*C), depth_score)."""
+        ctx.im2col_step = im2col_step
+        ctx.set_materialize_grads(False)
+        output, depth_score = ext_module.dfa3d_fused_forward(
+            value, value_dpt_dist, value_spatial_shapes, value_level_start_index, sampling_locations,
+            attention_weights, im2col_step=ctx.im2col_step, need_depth_score=return_depth_score)
+        ctx.save_for_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                              sampling_locations, attention_weights)
+        return output, depth_score
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output, grad_depth_score_=None):
+        # As in the reference (…attn_function.py:315-316) a gradient flowing into the returned
+        # depth_score is not supported.  Gradients are not materialised, so the usual case (nothing
+        # consumes depth_score's gradient) arrives as None and costs no device synchronisation.
+        if grad_depth_score_ is not None and grad_depth_score_.sum() != 0.0:
+            raise NotImplementedError
+        value, dist, shapes, lsi, loc, attn = ctx.saved_tensors
+        if grad_output is None:
+            return (None,) * 8
+        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_dist = torch.zeros(dist.shape, dtype=torch.float32, device=dist.device)
+        grad_sampling_loc = torch.empty_like(loc)
+        grad_attn_weight = torch.empty_like(attn)
+        ext_module.dfa3d_fused_backward(
+            value, dist, shapes, lsi, loc, attn, grad_output.contiguous(), grad_value, grad_dist,
+            grad_sampling_loc, grad_attn_weight, im2col_step=ctx.im2col_step)
+        return grad_value, grad_dist, None, None, grad_sampling_loc, grad_attn_weight, None, None
+
+
+def _fp32_variant(cls, name):
+    """Same Function with inputs cast to float32 when autocast is active."""
+    fwd = torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float32)(cls.forward)
+    bwd = torch.amp.custom_bwd(device_type="cuda")(cls.backward)
+    return type(name, (Function,), {"forward": staticmethod(fwd), "backward": staticmethod(bwd)})
+
+
+MultiScaleDepthScoreSampleFunction_fp32 = _fp32_variant(
+    MultiScaleDepthScoreSampleFunction, "MultiScaleDepthScoreSampleFunction_fp32")
+WeightedMultiScaleDeformableAttnFunction_fp32 = _fp32_variant(
+    WeightedMultiScaleDeformableAttnFunction, "WeightedMultiScaleDeformableAttnFunction_fp32")
+MultiScale3DDeformableAttnFunction_fp32 = _fp32_variant(
+    MultiScale3DDeformableAttnFunction, "MultiScale3DDeformableAttnFunction_fp32")

@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the DFA3D operator hot path: fused forward + fused backward, sampled points / s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one forward + backward of the operator over one batch of seeded synthetic inputs
+(default workload ``cfg2``: 6 cameras, BEVFormer-base level shapes, 10 000 queries, 8 heads x 32
+channels, 4 levels x 8 points, 64 depth bins, fp32, ~15 % of the points outside the image).  With
+N > 1 every rank owns its own batch of camera frames (weak scaling, no data-path collective: frames
+are independent); the job value is the points of all ranks over the slowest rank's time.
+
+Printed by rank 0: ONE JSON line with
+  value      device-resident throughput (inputs in HBM, CUDA-event timed, max over ranks)
+  e2e        the same step through the public autograd API from pinned HOST buffers, host<->device
+             copies inside the timed region
+  roofline   the dominant kernel (backward) against the measured HBM copy bandwidth
+  cpu_baseline  the CPU oracle (C + OpenMP port of the reference kernels) on a bounded sample
+``--impl reference`` times the reference's own CUDA op (unmodified sources built for sm_100a into
+oracle/_ref) through its own one-stage autograd Function on the same workload; when that build is
+absent it times the CPU oracle port instead and says so.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [os.path.join(ROOT, "3d-deformable-attention_b200")]
+
+import torch  # noqa: E402
+import torch.distributed as dist_  # noqa: E402
+
+# DRAM bytes per launch from the committed ncu captures (dram__bytes_read.sum + dram__bytes_write.sum),
+# see profiles/.  Keyed by workload; None = not captured.
+NCU_DRAM_TRAFFIC = {
+    "cfg2": {"backward": None, "forward": None},
+}
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks: sampled through NVML (read-only) while the timed region runs
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # NVML missing: report nulls, do not fail the bench
+            log("clock sampling unavailable:", e)
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if r & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def start(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        if self._thr:
+            self._stop.set()
+            self._thr.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------------------------
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def cpu_baseline(w, budget_cameras=1):
+    """CPU oracle (C + OpenMP port of the reference kernels), fp32, fwd+bwd, on `budget_cameras`
+    cameras of the workload.  Returns the cpu_baseline object."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import dfa3d_oracle as O
+    from dfa3d_b200 import workloads as wl
+    ws = w.with_(B=budget_cameras)
+    d = wl.make_inputs(ws, head_repeat=True)
+    n = {k: v.numpy() for k, v in d.items()}
+    O.lib()
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        out, ds = O.dfa3d_forward(n["value"], n["dist"], n["shapes"], n["lsi"], n["loc"], n["attn"])
+        O.dfa3d_backward(n["value"], n["dist"], n["shapes"], n["lsi"], n["loc"], n["attn"],
+                         n["grad_out"], depth_score=ds)
+        reps += 1
+        el = time.perf_counter() - t0
+        if el > 10.0 or reps >= 5:
+            break
+    assert np.isfinite(out).all()
+    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    return {"value": ws.points * reps / el, "unit": "sampled points/s", "cores": cores, "kind": "port",
+            "sample": f"{budget_cameras} of {w.B} cameras of {w.name} (same per-camera shapes), fp32, "
+                      f"fwd+bwd, {reps} repetitions in {el:.1f} s, C+OpenMP port of the reference "
+                      f"kernels on {cores} host threads"}
+
+
+# ----------------------------------------------------------------------------------------------
+class OursRunner:
+    """Device-resident step: fused forward, zeroing of the two accumulated gradients, fused backward,
+    through the extension-level API (raw C-ABI calls on preallocated tensors)."""
+    launches_per_step = 2
+
+    def __init__(self, w, t):
+        from dfa3d_b200 import ext
+        self.ext, self.t, self.w = ext, t, w
+        self.value = t["value"].bfloat16() if w.value_dtype == "bf16" else t["value"]
+        self.dist = t["dist"].bfloat16() if w.value_dtype == "bf16" else t["dist"]
+        self.gv = torch.zeros_like(t["value"]); self.gd = torch.zeros_like(t["dist"])
+        self.gl = torch.empty_like(t["loc"]); self.ga = torch.empty_like(t["attn"])
+
+    def forward(self):
+        t = self.t
+        self.out, _ = self.ext.dfa3d_fused_forward(self.value, self.dist, t["shapes"], t["lsi"], t["loc"],
+                                                   t["attn"], 64, need_depth_score=False)
+
+    def zero(self):
+        self.gv.zero_(); self.gd.zero_()
+
+    def backward(self):
+        t = self.t
+        self.ext.dfa3d_fused_backward(self.value, self.dist, t["shapes"], t["lsi"], t["loc"], t["attn"],
+                                      t["grad_out"], self.gv, self.gd, self.gl, self.ga, 64)
+
+    def e2e_step(self, host, pinned_out):
+        """Public autograd API from pinned host buffers: H2D of every input, forward, backward, D2H of
+        the output and of all four gradients."""
+        import dfa3d_b200 as M
+        dev = self.t["loc"].device
+        value = host["value"].to(dev, non_blocking=True).requires_grad_(True)
+        dist = host["dist"].to(dev, non_blocking=True).requires_grad_(True)
+        loc = host["loc"].to(dev, non_blocking=True).requires_grad_(True)
+        attn = host["attn"].to(dev, non_blocking=True).requires_grad_(True)
+        go = host["grad_out"].to(dev, non_blocking=True)
+        out, _ = M.MultiScale3DDeformableAttnFunction.apply(value, dist, self.t["shapes"], self.t["lsi"],
+                                                            loc, attn, 64, False)
+        out.backward(go)
+        for k, g in (("out", out.detach()), ("grad_value", value.grad), ("grad_dist", dist.grad),
+                     ("grad_loc", loc.grad), ("grad_attn", attn.grad)):
+            pinned_out[k].copy_(g, non_blocking=True)
+
+
+class ReferenceRunner:
+    """The reference's CUDA op through its own one-stage autograd Function (dist repeated per head, as
+    its kernels require; the repeat itself is not timed)."""
+    launches_per_step = 4
+
+    def __init__(self, w, t, ref):
+        self.ref, self.t, self.w = ref, t, w
+        self.dist_h = t["dist"].view(w.B, w.N, 1, w.D).repeat(1, 1, w.H, 1)
+        self.leaves = [t["value"].clone().requires_grad_(True), self.dist_h.requires_grad_(True),
+                       t["loc"].clone().requires_grad_(True), t["attn"].clone().requires_grad_(True)]
+
+    def forward(self):
+        for x in self.leaves:
+            x.grad = None
+        lv, t = self.leaves, self.t
+        self.out, _ = self.ref.MultiScale3DDeformableAttnFunction_fp32.apply(
+            lv[0], lv[1], t["shapes"], t["lsi"], lv[2], lv[3], 64)
+
+    def zero(self):
+        pass   # the reference Function zeroes inside backward
+
+    def backward(self):
+        self.out.backward(self.t["grad_out"])
+
+    def e2e_step(self, host, pinned_out):
+        dev = self.t["loc"].device
+        w = self.w
+        value = host["value"].to(dev, non_blocking=True).requires_grad_(True)
+        dist = host["dist"].to(dev, non_blocking=True).view(w.B, w.N, 1, w.D).repeat(1, 1, w.H, 1)
+        dist.requires_grad_(True)
+        loc = host["loc"].to(dev, non_blocking=True).requires_grad_(True)
+        attn = host["attn"].to(dev, non_blocking=True).requires_grad_(True)
+        go = host["grad_out"].to(dev, non_blocking=True)
+        out, _ = self.ref.MultiScale3DDeformableAttnFunction_fp32.apply(
+            value, dist, self.t["shapes"], self.t["lsi"], loc, attn, 64)
+        out.backward(go)
+        for k, g in (("out", out.detach()), ("grad_value", value.grad), ("grad_dist", dist.grad.sum(2)),
+                     ("grad_loc", loc.grad), ("grad_attn", attn.grad)):
+            pinned_out[k].copy_(g, non_blocking=True)
+
+
+# ----------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+
+    from dfa3d_b200 import workloads as wl
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world != a.gpus:
+        log(f"note: --gpus {a.gpus} but WORLD_SIZE={world}; using WORLD_SIZE")
+    w = wl.WORKLOADS[a.workload]
+
+    ref = None
+    if a.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        try:
+            import warnings
+            warnings.simplefilter("ignore")
+            import build_ref
+            ref = build_ref.load()
+        except Exception as e:
+            log("reference CUDA op unavailable:", e)
+        if ref is None or not torch.cuda.is_available():
+            # CPU arm: the oracle port on the host cores, rank 0 only
+            if rank == 0:
+                cb = cpu_baseline(w, 1)
+                line = {"metric": "DFA3D fwd+bwd sampled points/s", "value": cb["value"],
+                        "unit": "sampled points/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+                        "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+                        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+                        "config": {"workload": w.name}, "cpu_baseline": cb,
+                        "e2e": {"value": cb["value"], "unit": cb["unit"], "h2d_bytes_per_step": 0,
+                                "d2h_bytes_per_step": 0},
+                        "note": "reference CUDA op build (oracle/_ref) not present: timed the CPU port"}
+                print(json.dumps(line), flush=True)
+            return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: dfa3d_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist_.init_process_group("nccl", device_id=dev)
+
+    d = wl.make_inputs(w, seed=w.seed + 1000 * rank)
+    t = {k: v.to(dev) for k, v in d.items()}
+    runner = OursRunner(w, t) if a.impl == "ours" else ReferenceRunner(w, t, ref)
+
+    def step(events=None):
+        if events is not None:
+            events[0].record()
+        runner.forward()
+        if events is not None:
+            events[1].record()
+        runner.zero()
+        if events is not None:
+            events[2].record()
+        runner.backward()
+        if events is not None:
+            events[3].record()
+
+    def barrier():
+        if world > 1:
+            dist_.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(a.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(a.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    t_begin.record()
+    for i in range(a.steps):
+        step(evs[i])
+    t_end.record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = t_begin.elapsed_time(t_end)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / a.steps
+    bwd_ms = sum(e[2].elapsed_time(e[3]) for e in evs) / a.steps
+    tm = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist_.all_reduce(tm, op=dist_.ReduceOp.MAX)
+    total_ms = float(tm.item())
+    ms_per_step = total_ms / a.steps
+    value = w.points * world / (ms_per_step * 1e-3)
+
+    # ---- end to end from pinned host buffers through the public API -------------------------
+    host = {k: d[k].pin_memory() for k in ("value", "dist", "loc", "attn", "grad_out")}
+    pinned_out = {"out": torch.empty(w.B, w.Q, w.H * w.C).pin_memory(),
+                  "grad_value": torch.empty_like(d["value"]).pin_memory(),
+                  "grad_dist": torch.empty_like(d["dist"]).pin_memory(),
+                  "grad_loc": torch.empty_like(d["loc"]).pin_memory(),
+                  "grad_attn": torch.empty_like(d["attn"]).pin_memory()}
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = sum(v.numel() * v.element_size() for v in pinned_out.values())
+    for _ in range(2):
+        runner.e2e_step(host, pinned_out)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.e2e_steps):
+        runner.e2e_step(host, pinned_out)
+    e1.record()
+    barrier()
+    em = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist_.all_reduce(em, op=dist_.ReduceOp.MAX)
+    e2e_ms = float(em.item()) / a.e2e_steps
+    assert torch.isfinite(pinned_out["out"]).all()
+
+    if rank == 0:
+        peak, peak_src = measured_peak_gbs()
+        fwd_b, bwd_b = w.algorithmic_bytes()
+        traffic = NCU_DRAM_TRAFFIC.get(w.name, {})
+        line = {
+            "metric": "DFA3D fwd+bwd sampled points/s", "value": value, "unit": "sampled points/s",
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 storage, f32 math" if w.value_dtype == "bf16" else "f32",
+            "data": "synthetic",
+            "config": {"workload": w.name, "cameras_per_gpu": w.B, "queries": w.Q, "heads": w.H,
+                       "channels": w.C, "levels": [list(x) for x in w.levels], "points": w.P,
+                       "depth_bins": w.D, "points_per_gpu_step": w.points,
+                       "l2": "inputs per step (%.0f MB) exceed the 126 MB L2; no explicit flush"
+                             % (fwd_b / 1e6)},
+            "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
+            "clocks": clocks,
+            "gpu_launches": runner.launches_per_step * a.steps,
+            "e2e": {"value": w.points * world / (e2e_ms * 1e-3), "unit": "sampled points/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "steps": a.e2e_steps},
+        }
+        if a.impl == "ours":
+            line["roofline"] = {
+                "kernel": "dfa3d_backward_kernel", "bound": "hbm",
+                "achieved": bwd_b / (bwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                "frac": bwd_b / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic.get("backward"),
+                "algorithmic_bytes": bwd_b, "peak_source": peak_src}
+            line["roofline_forward"] = {
+                "kernel": "dfa3d_forward_kernel", "bound": "hbm",
+                "achieved": fwd_b / (fwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic.get("forward"),
+                "algorithmic_bytes": fwd_b}
+            line["roofline_step"] = {"frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak,
+                                     "algorithmic_bytes": fwd_b + bwd_b}
+            if world == 1 and not a.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline(w, 1)
+        else:
+            line["impl"] = "reference"
+            line["reference_kind"] = ("reference CUDA op (unmodified sources, sm_100a build in "
+                                      "oracle/_ref) through its own autograd Function, same GPU")
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist_.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

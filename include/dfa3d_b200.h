@@ -1,0 +1,121 @@
+/* dfa3d_b200 -- C ABI of the B200 (sm_100a) DFA3D operator library (libdfa3d_b200.so).
+ *
+ * The library replaces the device side of the reference's `dfa3D._ext` extension module.  Every entry
+ * point takes raw DEVICE pointers, a problem descriptor of plain integers and a CUDA stream; it
+ * allocates nothing, keeps no pointer after returning, launches asynchronously on `stream` and returns
+ * DFA3D_OK or a negative error code (never aborts, never traps the GPU).  `dfa3d_last_error()` gives
+ * the message of the calling thread's last failure.
+ *
+ * Tensor layouts are the reference's (all contiguous, row-major):
+ *   value        (B, N, H, C)           fp32 or bf16        N = sum over levels of h_l * w_l
+ *   dist         (B, N, H, D) or (B, N, D) shared by all heads   fp32 or bf16, per-pixel depth distribution
+ *   loc3 / loc2  (B, Q, H, L, P, 3|2)   fp32   (x, y[, z]) in units of the level's width/height/depth
+ *   attn         (B, Q, H, L, P)        fp32
+ *   depth_score  (B, Q, H, L, P, 4)     fp32   corner order 0=(y0,x0) 1=(y0,x1) 2=(y1,x1) 3=(y1,x0)
+ *   out          (B, Q, H*C)            fp32
+ *   spatial_shapes (L, 3|2) int64 = (h, w[, d]) and level_start_index (L) int64, both in DEVICE
+ *   memory: the kernels read them there, as the reference's kernels do
+ *   (DFA3D/dfa3D/ops/csrc/common/cuda/wms_deform_attn_cuda_kernel.cuh:273-276).
+ * Gradients are fp32 whatever the storage type of value/dist.
+ */
+#ifndef DFA3D_B200_H_
+#define DFA3D_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DFA3D_ABI_VERSION 1
+
+#define DFA3D_OK 0
+#define DFA3D_ERR_INVALID_ARGUMENT (-1) /* null pointer, non-positive size, bad enum, misaligned pointer */
+#define DFA3D_ERR_UNSUPPORTED (-2)      /* shape outside what the kernels cover (see DFA3D_MAX_*) */
+#define DFA3D_ERR_CUDA (-3)             /* a CUDA runtime call or the launch failed */
+
+#define DFA3D_DTYPE_F32 0
+#define DFA3D_DTYPE_BF16 1
+
+#define DFA3D_MAX_LEVELS 32   /* L */
+#define DFA3D_MAX_CHANNELS 1024 /* C; reference kernels for C > 1024 are themselves broken
+                                   (wms_deform_attn_cuda_kernel.cuh:968-971 pass un-offset pointers) */
+
+/* Problem descriptor shared by all entry points (plain integers, fixed widths, no padding). */
+typedef struct dfa3d_problem {
+  int32_t B;  /* batch * cameras */
+  int32_t N;  /* pixels over all levels */
+  int32_t H;  /* heads */
+  int32_t C;  /* channels per head (multiple of 4 for fp32 value, of 8 for bf16) */
+  int32_t D;  /* depth bins = channel count of dist */
+  int32_t L;  /* levels */
+  int32_t Q;  /* queries */
+  int32_t P;  /* sampling points per level */
+  int32_t value_dtype;       /* DFA3D_DTYPE_* of `value` */
+  int32_t dist_dtype;        /* DFA3D_DTYPE_* of `dist`  */
+  int64_t dist_head_stride;  /* elements between heads of one pixel in `dist`: D for (B,N,H,D);
+                                0 for (B,N,D) shared by all heads (then grad_dist is (B,N,D) too,
+                                already summed over heads) */
+} dfa3d_problem;
+
+/* ABI version of the loaded library (== DFA3D_ABI_VERSION of the header it was built from). */
+int dfa3d_abi_version(void);
+
+/* Message of the last error raised on the calling thread ("" if none). */
+const char *dfa3d_last_error(void);
+
+/* Depth-score sampling, forward.  Replaces ms_depth_score_sample_forward
+ * (DFA3D/dfa3D/ops/csrc/pybind.cpp:55-59 -> cuda/ms_depth_score_sample_cuda.cu:49-111 ->
+ * common/cuda/ms_depth_score_sample_cuda_kernel.cuh:94-148).
+ * Writes every element of depth_score (no pre-zeroing needed).  shapes3 is (L,3). */
+int dfa3d_depth_score_forward(const dfa3d_problem *p, const void *dist, const int64_t *shapes3,
+                              const int64_t *level_start, const float *loc3, float *depth_score,
+                              void *stream);
+
+/* Depth-score sampling, backward.  Replaces ms_depth_score_sample_backward
+ * (pybind.cpp:60-66 -> ms_depth_score_sample_cuda.cu:137-202 -> kernel.cuh:242-327).
+ * grad_dist is ACCUMULATED into with atomics (caller zeroes it, as the reference's Function does);
+ * grad_loc3 (B,Q,H,L,P,3) is overwritten: (0, 0, dL/dz). */
+int dfa3d_depth_score_backward(const dfa3d_problem *p, const void *dist, const int64_t *shapes3,
+                               const int64_t *level_start, const float *loc3,
+                               const float *grad_depth_score, float *grad_dist, float *grad_loc3,
+                               void *stream);
+
+/* Depth-weighted multi-scale deformable attention, forward, depth_score given.  Replaces
+ * wms_deform_attn_forward (pybind.cpp:43-47 -> cuda/wms_deform_attn_cuda.cu:213-288 ->
+ * common/cuda/wms_deform_attn_cuda_kernel.cuh:240-303).  shapes2 is (L,2), loc2 is (...,2).
+ * Writes every element of out. */
+int dfa3d_wms_attn_forward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
+                           const int64_t *level_start, const float *loc2, const float *attn,
+                           const float *depth_score, float *out, void *stream);
+
+/* Depth-weighted attention, backward.  Replaces wms_deform_attn_backward (pybind.cpp:48-54 ->
+ * wms_deform_attn_cuda.cu:291-370 -> kernel.cuh:305-419 and its five sibling kernels).
+ * grad_value (B,N,H,C) fp32 is ACCUMULATED into (caller zeroes it); grad_loc2, grad_attn and
+ * grad_depth_score are overwritten. */
+int dfa3d_wms_attn_backward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
+                            const int64_t *level_start, const float *loc2, const float *attn,
+                            const float *depth_score, const float *grad_out, float *grad_value,
+                            float *grad_loc2, float *grad_attn, float *grad_depth_score,
+                            void *stream);
+
+/* One-stage forward: both reference kernels in one launch, depth_score never leaves the SM unless
+ * depth_score_out is non-null.  Replaces the forward of MultiScale3DDeformableAttnFunction_fp32
+ * (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/
+ *  multi_scale_3ddeformable_attn_function.py:279-305).  shapes3 is (L,3), loc3 is (...,3). */
+int dfa3d_fused_forward(const dfa3d_problem *p, const void *value, const void *dist,
+                        const int64_t *shapes3, const int64_t *level_start, const float *loc3,
+                        const float *attn, float *out, float *depth_score_out, void *stream);
+
+/* One-stage backward: replaces the backward of the same Function (:306-352), i.e. both reference
+ * backward kernels, the slice copies and four of its six memsets.  grad_value and grad_dist are
+ * ACCUMULATED into (caller zeroes them); grad_loc3 (x, y and z parts) and grad_attn are overwritten. */
+int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *dist,
+                         const int64_t *shapes3, const int64_t *level_start, const float *loc3,
+                         const float *attn, const float *grad_out, float *grad_value,
+                         float *grad_dist, float *grad_loc3, float *grad_attn, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DFA3D_B200_H_ */

@@ -20,14 +20,18 @@
 
 #define REAL float
 #define SUF(name) CAT(name, _f32)
+#define FMA fmaf
 #include "dfa3d_oracle_body.inc"
 #undef REAL
 #undef SUF
+#undef FMA
 
 #define REAL double
 #define SUF(name) CAT(name, _f64)
+#define FMA fma
 #include "dfa3d_oracle_body.inc"
 #undef REAL
 #undef SUF
+#undef FMA
 
 int dfa3d_oracle_abi_version(void) { return 1; }

@@ -1,0 +1,89 @@
+"""The C-ABI library loads without a GPU, exports every symbol the public header declares, and its
+host-side validation answers with error codes (no compute call is made here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "dfa3d_b200.h")
+
+
+def declared_symbols():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(dfa3d_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for n in ("dfa3d_depth_score_forward", "dfa3d_depth_score_backward", "dfa3d_wms_attn_forward",
+              "dfa3d_wms_attn_backward", "dfa3d_fused_forward", "dfa3d_fused_backward",
+              "dfa3d_last_error", "dfa3d_abi_version"):
+        assert n in names
+
+
+def test_library_exports_every_declared_symbol(lib_built):
+    lib = ctypes.CDLL(lib_built)
+    for n in declared_symbols():
+        assert hasattr(lib, n), f"{n} declared in include/dfa3d_b200.h but not exported"
+
+
+def test_binding_table_matches_header(lib_built):
+    from dfa3d_b200 import _lib
+    declared = set(declared_symbols()) - {"dfa3d_last_error", "dfa3d_abi_version"}
+    assert declared <= set(_lib.ENTRY_POINTS) , declared - set(_lib.ENTRY_POINTS)
+    assert _lib.load().dfa3d_abi_version() == _lib.ABI_VERSION
+
+
+def test_problem_struct_layout():
+    from dfa3d_b200 import _lib
+    assert ctypes.sizeof(_lib.Problem) == 10 * 4 + 8
+    assert _lib.Problem.dist_head_stride.offset == 40
+
+
+def test_validation_returns_codes_not_crashes(lib_built):
+    from dfa3d_b200 import _lib
+    lib = _lib.load()
+    ok = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, 0, 0, 2)
+    # null descriptor
+    assert lib.dfa3d_fused_forward(None, *([None] * 9)) == -1
+    assert b"null" in lib.dfa3d_last_error()
+    # null tensor pointer
+    assert lib.dfa3d_fused_forward(ctypes.byref(ok), *([None] * 9)) == -1
+    assert b"value" in lib.dfa3d_last_error()
+    # too many levels -> unsupported
+    bad = _lib.Problem(1, 4, 1, 4, 2, 33, 1, 1, 0, 0, 2)
+    assert lib.dfa3d_fused_forward(ctypes.byref(bad), *([None] * 9)) == -2
+    # bad enum
+    bad = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, 7, 0, 2)
+    assert lib.dfa3d_fused_forward(ctypes.byref(bad), *([None] * 9)) == -1
+    # bad head stride
+    bad = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, 0, 0, 3)
+    assert lib.dfa3d_fused_backward(ctypes.byref(bad), *([None] * 12)) == -1
+    # misaligned value pointer
+    assert lib.dfa3d_fused_forward(ctypes.byref(ok), 8, 16, 16, 16, 16, 16, 16, None, None) == -1
+    assert b"aligned" in lib.dfa3d_last_error()
+    # empty problem: nothing to do, OK without touching the pointers
+    empty = _lib.Problem(0, 4, 1, 4, 2, 1, 0, 1, 0, 0, 2)
+    for name, n in _lib.ENTRY_POINTS.items():
+        assert getattr(lib, name)(ctypes.byref(empty), *([None] * n)) == 0, name
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        _lib.call("dfa3d_fused_forward", ok, *([None] * 9))
+
+
+def test_shim_rejects_cpu_tensors_like_the_reference(lib_built):
+    import torch
+    from dfa3d_b200 import ext, MultiScale3DDeformableAttnFunction
+    from dfa3d_b200 import workloads as wl
+    d = wl.make_inputs(wl.WORKLOADS["tiny"])
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        ext.dfa3d_fused_forward(d["value"], d["dist"], d["shapes"], d["lsi"], d["loc"], d["attn"], 64)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        MultiScale3DDeformableAttnFunction.apply(d["value"], d["dist"], d["shapes"], d["lsi"], d["loc"],
+                                                 d["attn"], 64)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        ext.wms_deform_attn_forward(d["value"], d["shapes"][:, :2].contiguous(), d["lsi"],
+                                    d["loc"][..., :2].contiguous(), d["attn"],
+                                    torch.zeros(*d["attn"].shape, 4), 64)
