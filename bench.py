@@ -231,6 +231,8 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cameras", type=int, default=0,
+                    help="override the workload's cameras per GPU (small cases for profiler captures)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
 
@@ -241,6 +243,8 @@ def main():
     if world != a.gpus:
         log(f"note: --gpus {a.gpus} but WORLD_SIZE={world}; using WORLD_SIZE")
     w = wl.WORKLOADS[a.workload]
+    if a.cameras > 0:
+        w = w.with_(B=a.cameras)
 
     ref = None
     if a.impl == "reference":
@@ -320,6 +324,17 @@ def main():
     value = w.points * world / (ms_per_step * 1e-3)
 
     # ---- end to end from pinned host buffers through the public API -------------------------
+    e2e = None
+    if a.e2e_steps > 0:
+        e2e = measure_e2e(a, w, d, dev, world, runner, barrier)
+
+    if rank == 0:
+        report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e)
+    if world > 1:
+        dist_.destroy_process_group()
+
+
+def measure_e2e(a, w, d, dev, world, runner, barrier):
     host = {k: d[k].pin_memory() for k in ("value", "dist", "loc", "attn", "grad_out")}
     pinned_out = {"out": torch.empty(w.B, w.Q, w.H * w.C).pin_memory(),
                   "grad_value": torch.empty_like(d["value"]).pin_memory(),
@@ -342,8 +357,13 @@ def main():
         dist_.all_reduce(em, op=dist_.ReduceOp.MAX)
     e2e_ms = float(em.item()) / a.e2e_steps
     assert torch.isfinite(pinned_out["out"]).all()
+    return {"value": w.points * world / (e2e_ms * 1e-3), "unit": "sampled points/s",
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+            "steps": a.e2e_steps}
 
-    if rank == 0:
+
+def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e):
+    if True:
         peak, peak_src = measured_peak_gbs()
         fwd_b, bwd_b = w.algorithmic_bytes()
         traffic = NCU_DRAM_TRAFFIC.get(w.name, {})
@@ -361,9 +381,7 @@ def main():
             "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
             "clocks": clocks,
             "gpu_launches": runner.launches_per_step * a.steps,
-            "e2e": {"value": w.points * world / (e2e_ms * 1e-3), "unit": "sampled points/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "steps": a.e2e_steps},
+            "e2e": e2e,
         }
         if a.impl == "ours":
             line["roofline"] = {
@@ -385,8 +403,6 @@ def main():
             line["reference_kind"] = ("reference CUDA op (unmodified sources, sm_100a build in "
                                       "oracle/_ref) through its own autograd Function, same GPU")
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist_.destroy_process_group()
 
 
 if __name__ == "__main__":
