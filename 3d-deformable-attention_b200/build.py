@@ -12,7 +12,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "dfa3d_b200", "libdfa3d_b200.so")
 SOURCES = ["dfa3d_forward.cu", "dfa3d_backward.cu", "dfa3d_capi.cu"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+INCLUDE = os.path.join(HERE, "..", "include")
+NVCC_FLAGS = ["-O3", "-I", INCLUDE, "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
 

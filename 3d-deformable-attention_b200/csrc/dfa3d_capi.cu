@@ -4,7 +4,7 @@
 #include <stdio.h>
 #include <string.h>
 
-#include "../../include/dfa3d_b200.h"
+#include "dfa3d_b200.h"
 #include "dfa3d_common.cuh"
 #include "dfa3d_launch.h"
 

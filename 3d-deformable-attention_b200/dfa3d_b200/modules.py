@@ -1,0 +1,212 @@
+"""mmcv-free restatement of the callers of the DFA3D operator in BEVFormer-DFA3D.
+
+  * ``MSDeformableAttention3D_DFA3D``  -- BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/
+    spatial_cross_attention.py:409-587 (and its parent's parameters/initialisation, :182-277)
+  * ``SpatialCrossAttention_DFA3D``    -- same file :616-751
+  * ``SCAEncoderLayer`` / ``SCAEncoderStack`` -- the cross-attention -> norm -> FFN -> norm part of one
+    BEVFormer encoder layer (…/modules/encoder.py:249-413 with the 'cross_attn', 'norm', 'ffn',
+    'norm' operation order), used for the training-step configuration.
+
+Parameter names, shapes and initialisation follow the reference so that its checkpoints load; the
+registry / config plumbing of mmcv is not reproduced.  Differences in how the operator is fed:
+the depth distribution is passed as (B, N, D) shared by all heads instead of being repeated per head
+(:497 in the reference), and the per-camera re-batching uses index tensors instead of Python loops.
+"""
+import math
+
+import torch
+import torch.nn as nn
+
+from .functions import MultiScale3DDeformableAttnFunction_fp32
+
+
+def assemble_sampling_locations(reference_points, offsets_uv, offsets_depth, spatial_shapes, depth_bins):
+    """Sampling locations from reference points and predicted offsets
+    (spatial_cross_attention.py:498-538).
+
+    reference_points (bs, Q, Z, 3) in [0,1] (x, y, depth); offsets_uv (bs, Q, H, L, P_all, 2) and
+    offsets_depth (bs, Q, H, L, P_all, 1) in pixels / bins; spatial_shapes (L, 2) = (h, w).
+    P_all = P * Z: the P_all sampling points of a level are split over the Z anchors of the pillar.
+    Returns (bs, Q, H, L, P_all, 3)."""
+    bs, Q, Z, three = reference_points.shape
+    assert three == 3
+    _, _, H, L, P_all, _ = offsets_uv.shape
+    assert P_all % Z == 0
+    normalizer = torch.stack([spatial_shapes[:, 1], spatial_shapes[:, 0],
+                              torch.full_like(spatial_shapes[:, 0], depth_bins)], -1).to(offsets_uv.dtype)
+    offsets = torch.cat([offsets_uv, offsets_depth], -1) / normalizer[None, None, None, :, None, :]
+    offsets = offsets.view(bs, Q, H, L, P_all // Z, Z, 3)
+    loc = reference_points[:, :, None, None, None, :, :] + offsets
+    return loc.view(bs, Q, H, L, P_all, 3)
+
+
+class MSDeformableAttention3D_DFA3D(nn.Module):
+    """3-D deformable attention over multi-level camera features and their depth distributions."""
+
+    def __init__(self, embed_dims=256, num_heads=8, num_levels=4, num_points=8, im2col_step=64,
+                 batch_first=True):
+        super().__init__()
+        if embed_dims % num_heads != 0:
+            raise ValueError(f"embed_dims must be divisible by num_heads, but got {embed_dims} and "
+                             f"{num_heads}")
+        self.embed_dims, self.num_heads = embed_dims, num_heads
+        self.num_levels, self.num_points = num_levels, num_points
+        self.im2col_step, self.batch_first = im2col_step, batch_first
+        self.sampling_offsets = nn.Linear(embed_dims, num_heads * num_levels * num_points * 2)
+        self.sampling_offsets_depth = nn.Linear(embed_dims, num_heads * num_levels * num_points)
+        self.attention_weights = nn.Linear(embed_dims, num_heads * num_levels * num_points)
+        self.value_proj = nn.Linear(embed_dims, embed_dims)
+        self.init_weights()
+
+    def init_weights(self):
+        """spatial_cross_attention.py:256-276 (u,v offsets, attention, value_proj) and :414-426 (depth
+        offsets)."""
+        H, L, P = self.num_heads, self.num_levels, self.num_points
+        nn.init.zeros_(self.sampling_offsets.weight)
+        thetas = torch.arange(H, dtype=torch.float32) * (2.0 * math.pi / H)
+        grid = torch.stack([thetas.cos(), thetas.sin()], -1)
+        grid = (grid / grid.abs().max(-1, keepdim=True)[0]).view(H, 1, 1, 2).repeat(1, L, P, 1)
+        scale = torch.arange(1, P + 1, dtype=torch.float32).view(1, 1, P, 1)
+        with torch.no_grad():
+            self.sampling_offsets.bias.copy_((grid * scale).view(-1))
+            nn.init.zeros_(self.sampling_offsets_depth.weight)
+            gd = ((thetas.cos() + thetas.sin()) / 2).view(H, 1, 1, 1).repeat(1, L, P, 1)
+            self.sampling_offsets_depth.bias.copy_((gd * scale).view(-1))
+            nn.init.zeros_(self.attention_weights.weight)
+            nn.init.zeros_(self.attention_weights.bias)
+            nn.init.xavier_uniform_(self.value_proj.weight)
+            nn.init.zeros_(self.value_proj.bias)
+
+    def forward(self, query, value, value_dpt_dist, reference_points, spatial_shapes, level_start_index,
+                query_pos=None, key_padding_mask=None):
+        """query (bs, Q, E); value (bs, N, E); value_dpt_dist (bs, N, D); reference_points
+        (bs, Q, Z, 3); spatial_shapes (L, 2) int64; level_start_index (L) int64.
+        Returns (output (bs, Q, E), weight_update (bs, Q, H, 1))  -- :428-583."""
+        if query_pos is not None:
+            query = query + query_pos
+        if not self.batch_first:
+            query, value = query.permute(1, 0, 2), value.permute(1, 0, 2)
+        bs, Q, _ = query.shape
+        _, N, _ = value.shape
+        H, L, P = self.num_heads, self.num_levels, self.num_points
+        D = value_dpt_dist.shape[-1]
+        value = self.value_proj(value)
+        if key_padding_mask is not None:
+            value = value.masked_fill(key_padding_mask[..., None], 0.0)
+        value = value.view(bs, N, H, -1)
+        off_uv = self.sampling_offsets(query).view(bs, Q, H, L, P, 2)
+        off_d = self.sampling_offsets_depth(query).view(bs, Q, H, L, P, 1)
+        attn = self.attention_weights(query).view(bs, Q, H, L * P).softmax(-1).view(bs, Q, H, L, P)
+        if reference_points.shape[-1] != 3:
+            raise ValueError("Last dim of reference_points must be 3 (x, y, depth), but got "
+                             f"{reference_points.shape[-1]} instead.")
+        loc = assemble_sampling_locations(reference_points, off_uv, off_d, spatial_shapes, D)
+        shapes3 = torch.cat([spatial_shapes, torch.full_like(spatial_shapes[:, :1], D)], -1).contiguous()
+        output, depth_score = MultiScale3DDeformableAttnFunction_fp32.apply(
+            value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
+            loc.contiguous(), attn.contiguous(), self.im2col_step)
+        # mean depth score of a point's four corners, weighted by the attention (:579)
+        weight_update = (depth_score.mean(-1) * attn).flatten(-2).sum(-1, keepdim=True)
+        if not self.batch_first:
+            output = output.permute(1, 0, 2)
+        return output, weight_update
+
+
+class SpatialCrossAttention_DFA3D(nn.Module):
+    """BEV queries attend to the cameras that see them (spatial_cross_attention.py:616-751)."""
+
+    def __init__(self, embed_dims=256, num_cams=6, dropout=0.1, deformable_attention=None,
+                 bev_h=200, bev_w=200, num_head=8, use_empty=False):
+        super().__init__()
+        self.embed_dims, self.num_cams = embed_dims, num_cams
+        self.bev_h, self.bev_w, self.num_head, self.use_empty = bev_h, bev_w, num_head, use_empty
+        self.deformable_attention = deformable_attention or MSDeformableAttention3D_DFA3D(embed_dims)
+        self.output_proj = nn.Linear(embed_dims, embed_dims)
+        self.dropout = nn.Dropout(dropout)
+        if use_empty:
+            self.empty_query = nn.Embedding(bev_h * bev_w * num_head, embed_dims)
+        nn.init.xavier_uniform_(self.output_proj.weight)
+        nn.init.zeros_(self.output_proj.bias)
+
+    @staticmethod
+    def rebatch_indexes(bev_mask):
+        """bev_mask (num_cams, bs, Q, Z) bool -> (index (num_cams, max_len) int64 padded with 0,
+        valid (num_cams, max_len) bool).  Like the reference (:703-707) the queries of a camera are
+        those that camera sees in batch element 0."""
+        hit = bev_mask[:, 0].sum(-1) > 0                                  # (cams, Q)
+        lens = hit.sum(-1)
+        max_len = int(lens.max())
+        order = torch.argsort((~hit).to(torch.int8), dim=-1, stable=True)  # seen queries first, in order
+        index = order[:, :max_len]
+        valid = torch.arange(max_len, device=hit.device)[None] < lens[:, None]
+        return index.masked_fill(~valid, 0), valid
+
+    def forward(self, query, key=None, value=None, value_dpt_dist=None, reference_points_cam=None,
+                bev_mask=None, spatial_shapes=None, level_start_index=None, residual=None,
+                query_pos=None):
+        """query (bs, Q, E); value (num_cams, N, bs, E) (`key` is accepted and, as in the reference,
+        not used by the attention); value_dpt_dist (num_cams, N, bs, D);
+        reference_points_cam (num_cams, bs, Q, Z, 3); bev_mask (num_cams, bs, Q, Z).
+        Returns (bs, Q, E)."""
+        inp_residual = query if residual is None else residual
+        if query_pos is not None:
+            query = query + query_pos
+        bs, Q, E = query.shape
+        cams = self.num_cams
+        Z = reference_points_cam.size(3)
+        index, valid = self.rebatch_indexes(bev_mask)                       # (cams, max_len)
+        max_len = index.shape[1]
+        vf = valid[None, :, :, None].to(query.dtype)
+        q_re = query[:, index] * vf                                         # (bs, cams, max_len, E)
+        ref = reference_points_cam.permute(1, 0, 2, 3, 4)                   # (bs, cams, Q, Z, 3)
+        ref_re = torch.gather(ref, 2, index[None, :, :, None, None].expand(bs, cams, max_len, Z, 3))
+        ref_re = ref_re * valid[None, :, :, None, None].to(ref.dtype)
+        N = value.shape[1]
+        value = value.permute(2, 0, 1, 3).reshape(bs * cams, N, E)
+        dist = value_dpt_dist.permute(2, 0, 1, 3).reshape(bs * cams, N, -1)
+        out, update_weight = self.deformable_attention(
+            query=q_re.reshape(bs * cams, max_len, E), value=value, value_dpt_dist=dist,
+            reference_points=ref_re.reshape(bs * cams, max_len, Z, 3), spatial_shapes=spatial_shapes,
+            level_start_index=level_start_index)
+        out = out.view(bs, cams, max_len, E)
+        if self.use_empty:
+            update_weight = update_weight.view(bs, cams, max_len, self.num_head, 1)
+            empty = self.empty_query.weight.view(self.bev_h * self.bev_w, self.num_head, E)[index]
+            out = out + ((1 - update_weight) * (empty[None] * vf[..., None])).mean(-2)
+        slots = torch.zeros_like(query)
+        slots.index_put_((torch.arange(bs, device=query.device)[:, None, None].expand(bs, cams, max_len),
+                          index[None].expand(bs, cams, max_len)), out * vf, accumulate=True)
+        count = (bev_mask.sum(-1) > 0).permute(1, 2, 0).sum(-1).clamp(min=1.0)
+        slots = self.output_proj(slots / count[..., None])
+        return self.dropout(slots) + inp_residual
+
+
+class SCAEncoderLayer(nn.Module):
+    """cross-attention -> LayerNorm -> FFN -> LayerNorm (encoder.py:389-411 operation order without the
+    temporal self-attention, which uses a different, 2-D operator)."""
+
+    def __init__(self, embed_dims=256, ffn_dims=512, num_cams=6, num_heads=8, num_levels=4, num_points=8,
+                 dropout=0.1):
+        super().__init__()
+        self.cross_attn = SpatialCrossAttention_DFA3D(
+            embed_dims, num_cams, dropout,
+            MSDeformableAttention3D_DFA3D(embed_dims, num_heads, num_levels, num_points))
+        self.norm1 = nn.LayerNorm(embed_dims)
+        self.ffn = nn.Sequential(nn.Linear(embed_dims, ffn_dims), nn.ReLU(inplace=True), nn.Dropout(dropout),
+                                 nn.Linear(ffn_dims, embed_dims), nn.Dropout(dropout))
+        self.norm2 = nn.LayerNorm(embed_dims)
+
+    def forward(self, query, **kw):
+        query = self.norm1(self.cross_attn(query, **kw))
+        return self.norm2(query + self.ffn(query))
+
+
+class SCAEncoderStack(nn.Module):
+    def __init__(self, num_layers=6, **layer_kw):
+        super().__init__()
+        self.layers = nn.ModuleList(SCAEncoderLayer(**layer_kw) for _ in range(num_layers))
+
+    def forward(self, query, **kw):
+        for layer in self.layers:
+            query = layer(query, **kw)
+        return query

@@ -1,0 +1,63 @@
+"""Data-parallel plumbing around the operator: one process per GPU, camera frames sharded over ranks.
+
+Every camera frame is independent in the forward and in the backward of the operator (all its tensors
+carry the leading batch*camera dimension), so the operator itself needs no collective.  What is
+needed across ranks: a partition of the frames that keeps the cameras of one frame together, the
+maximum over ranks of a device-measured time, and -- for training configurations -- the all-reduce of
+the projection-layer gradients (the reference gets this from mmcv's DistributedDataParallel wrapper,
+BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/apis/mmdet_train.py:71-79).
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_frames(num_frames, world_size, rank):
+    """Contiguous, balanced partition of `num_frames` frames.  Returns range(start, stop); the first
+    `num_frames % world_size` ranks get one frame more."""
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside [0, {world_size})")
+    base, extra = divmod(num_frames, world_size)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def shard_cameras(num_frames, cams_per_frame, world_size, rank):
+    """Slice of the flattened (frame, camera) batch dimension owned by `rank`: whole frames only."""
+    fr = shard_frames(num_frames, world_size, rank)
+    return slice(fr.start * cams_per_frame, fr.stop * cams_per_frame)
+
+
+def max_over_ranks(value, device=None, group=None):
+    """Maximum of a per-rank scalar (a device-measured duration) over the process group."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())
+
+
+def allreduce_gradients(params, group=None, bucket_bytes=32 << 20):
+    """Average the gradients of `params` over the group in flat buckets (one collective per bucket:
+    sized for launch latency, NVSwitch gives every pair full bandwidth)."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return 0
+    world = dist.get_world_size(group)
+    if world == 1:
+        return 0
+    grads = [p.grad for p in params if p.grad is not None]
+    buckets, cur, cur_bytes = [], [], 0
+    for g in grads:
+        nb = g.numel() * g.element_size()
+        if cur and (cur_bytes + nb > bucket_bytes or g.dtype != cur[0].dtype):
+            buckets.append(cur); cur, cur_bytes = [], 0
+        cur.append(g); cur_bytes += nb
+    if cur:
+        buckets.append(cur)
+    for b in buckets:
+        flat = torch.cat([g.reshape(-1) for g in b])
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        flat.div_(world)
+        off = 0
+        for g in b:
+            g.copy_(flat[off:off + g.numel()].view_as(g)); off += g.numel()
+    return len(buckets)

@@ -36,7 +36,9 @@ import torch.distributed as dist_  # noqa: E402
 # DRAM bytes per launch from the committed ncu captures (dram__bytes_read.sum + dram__bytes_write.sum),
 # see profiles/.  Keyed by workload; None = not captured.
 NCU_DRAM_TRAFFIC = {
-    "cfg2": {"backward": None, "forward": None},
+    # profiles/dfa3d_forward_backward_cfg2_2cameras_ncu_full.md: 2-camera capture x 3 (cameras are
+    # independent, traffic grows in proportion)
+    "cfg2": {"forward": 3 * (164.162560e6 + 18.415104e6), "backward": 3 * (389.944576e6 + 198.461696e6)},
 }
 
 
@@ -363,7 +365,7 @@ def measure_e2e(a, w, d, dev, world, runner, barrier):
 
 
 def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e):
-    if True:
+    if True:  # noqa
         peak, peak_src = measured_peak_gbs()
         fwd_b, bwd_b = w.algorithmic_bytes()
         traffic = NCU_DRAM_TRAFFIC.get(w.name, {})

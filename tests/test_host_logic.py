@@ -1,0 +1,139 @@
+"""Host-side logic that needs no GPU: location assembly, per-camera re-batching, module
+initialisation, the dfa3D drop-in package, frame sharding and the world_size-2 gloo path."""
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from dfa3d_b200 import modules, sharding
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG_DIR = os.path.join(ROOT, "3d-deformable-attention_b200")
+
+
+def test_assemble_sampling_locations_matches_loops():
+    g = torch.Generator().manual_seed(0)
+    bs, Q, H, L, Z, P = 2, 3, 2, 2, 4, 2
+    ref = torch.rand(bs, Q, Z, 3, generator=g)
+    ouv = torch.randn(bs, Q, H, L, P * Z, 2, generator=g)
+    od = torch.randn(bs, Q, H, L, P * Z, 1, generator=g)
+    shapes = torch.tensor([[6, 9], [3, 5]])
+    D = 7
+    got = modules.assemble_sampling_locations(ref, ouv, od, shapes, D)
+    assert got.shape == (bs, Q, H, L, P * Z, 3)
+    for b in range(bs):
+        for q in range(Q):
+            for h in range(H):
+                for l in range(L):
+                    for j in range(P * Z):
+                        z = j % Z          # the points of a level cycle through the anchors
+                        hh, ww = shapes[l].tolist()
+                        exp = torch.stack([ref[b, q, z, 0] + ouv[b, q, h, l, j, 0] / ww,
+                                           ref[b, q, z, 1] + ouv[b, q, h, l, j, 1] / hh,
+                                           ref[b, q, z, 2] + od[b, q, h, l, j, 0] / D])
+                        torch.testing.assert_close(got[b, q, h, l, j], exp)
+
+
+def test_rebatch_indexes_matches_reference_loops():
+    g = torch.Generator().manual_seed(1)
+    cams, bs, Q, Z = 3, 2, 17, 4
+    mask = torch.rand(cams, bs, Q, Z, generator=g) > 0.8
+    mask[2] = False                       # a camera that sees nothing
+    index, valid = modules.SpatialCrossAttention_DFA3D.rebatch_indexes(mask)
+    lens = []
+    for i in range(cams):                 # spatial_cross_attention.py:703-707
+        idx = mask[i][0].sum(-1).nonzero().squeeze(-1)
+        lens.append(len(idx))
+        assert index[i, :len(idx)].tolist() == idx.tolist()
+        assert valid[i].tolist() == [True] * len(idx) + [False] * (index.shape[1] - len(idx))
+    assert index.shape[1] == max(lens)
+
+
+def test_module_initialisation_follows_reference():
+    m = modules.MSDeformableAttention3D_DFA3D(embed_dims=64, num_heads=8, num_levels=2, num_points=4)
+    assert not m.sampling_offsets.weight.any() and not m.attention_weights.weight.any()
+    b = m.sampling_offsets.bias.view(8, 2, 4, 2)
+    # head 0 points along +x, scaled by the point index (1..P)
+    torch.testing.assert_close(b[0, 0, :, 0], torch.arange(1.0, 5.0))
+    torch.testing.assert_close(b[0, 0, :, 1], torch.zeros(4))
+    bd = m.sampling_offsets_depth.bias.view(8, 2, 4)
+    th = 2 * math.pi / 8
+    torch.testing.assert_close(bd[1, 1, 2], torch.tensor((math.cos(th) + math.sin(th)) / 2 * 3))
+    names = {n for n, _ in m.named_parameters()}
+    for n in ("sampling_offsets.weight", "sampling_offsets_depth.bias", "attention_weights.weight",
+              "value_proj.weight"):
+        assert n in names                 # same parameter names as the reference module
+
+
+def test_dfa3D_drop_in_package_exposes_reference_names(lib_built):
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "from dfa3D import ext_loader\n"
+        "ext = ext_loader.load_ext('_ext', ['wms_deform_attn_backward', 'wms_deform_attn_forward',"
+        " 'ms_depth_score_sample_forward', 'ms_depth_score_sample_backward'])\n"
+        "from dfa3D.ops.multi_scale_3D_deform_attn import (WeightedMultiScaleDeformableAttnFunction,"
+        " MultiScaleDepthScoreSampleFunction, MultiScale3DDeformableAttnFunction)\n"
+        "from dfa3D.ops import MultiScaleDepthScoreSampleFunction as A\n"
+        "assert A is MultiScaleDepthScoreSampleFunction\n"
+        "try:\n ext_loader.load_ext('_ext', ['nope'])\nexcept AssertionError as e:\n assert 'miss in module' in str(e)\n"
+        "else:\n raise SystemExit('load_ext accepted a missing function')\n"
+        "print('ok')\n" % PKG_DIR)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr
+
+
+def test_shard_frames_partitions_everything():
+    for n in (1, 6, 8, 48):
+        for world in (1, 2, 3, 8):
+            got = [i for r in range(world) for i in sharding.shard_frames(n, world, r)]
+            assert got == list(range(n))
+            sizes = [len(sharding.shard_frames(n, world, r)) for r in range(world)]
+            assert max(sizes) - min(sizes) <= 1
+    assert sharding.shard_cameras(8, 6, 4, 1) == slice(12, 24)
+    with pytest.raises(ValueError):
+        sharding.shard_frames(4, 2, 2)
+
+
+def _gloo_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # frames of a global batch are split with whole frames per rank
+        frames = sharding.shard_frames(5, world, rank)
+        t = sharding.max_over_ranks(1.0 + rank)                 # slowest rank's time
+        lin = torch.nn.Linear(3, 2)
+        with torch.no_grad():
+            lin.weight.fill_(1.0); lin.bias.fill_(0.0)
+        x = torch.full((4, 3), float(rank + 1))
+        lin(x).sum().backward()
+        nb = sharding.allreduce_gradients(list(lin.parameters()), bucket_bytes=16)
+        q.put((rank, list(frames), t, lin.weight.grad.clone(), lin.bias.grad.clone(), nb))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_world_size_2_gloo_sharding_and_gradient_allreduce():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_gloo_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted((q.get(timeout=120) for _ in range(world)), key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res[0][1] + res[1][1] == [0, 1, 2, 3, 4]
+    assert res[0][2] == res[1][2] == 2.0
+    # rank r's weight grad is 4*(r+1) per element: the average over the two ranks is 6
+    for r in res:
+        torch.testing.assert_close(r[3], torch.full((2, 3), 6.0))
+        torch.testing.assert_close(r[4], torch.full((2,), 4.0))
+        assert r[5] >= 2                                        # tiny buckets -> several collectives
