@@ -21,11 +21,6 @@ namespace dfa3d {
 
 enum BwdMode { kFusedBwd = 0, kGivenDepthScoreBwd = 1 };
 
-struct __align__(8) RowEntryB {
-  int off;
-  float wgt;
-};
-
 // Per-lane state of one sampling point that the epilogue needs.
 struct PointState {
   PointGeo g;
@@ -36,9 +31,8 @@ struct PointState {
 };
 
 template <typename DT, int MODE>
-__device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, long long item, int j,
-                                          int b, int h, PointState &s, float (&wgt)[4],
-                                          int (&off)[4]) {
+__device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, const ItemCtx &c, int j,
+                                          PointState &s, float (&wgt)[4], int (&off)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     s.ds[k] = 0.f; s.bw[k] = 0.f; s.lo[k] = 0.f; s.hi[k] = 0.f; wgt[k] = 0.f; off[k] = -1;
@@ -47,27 +41,26 @@ __device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, 
   s.live = false; s.aw = 0.f; s.g.ok2 = false; s.g.ok3 = false;
   if (j >= a.LP) return;
   const int l = j / a.P;
-  const long long pt = item * a.LP + j;
-  const float *lp = a.loc + pt * a.loc_stride;
+  const float *lp = c.loc + j * a.loc_stride;
   const float x = __ldg(lp), y = __ldg(lp + 1);
   const float z = (MODE == kFusedBwd) ? __ldg(lp + 2) : 0.f;
-  s.aw = __ldg(a.attn + pt);
+  s.aw = __ldg(c.attn + j);
   s.g = point_geometry(x, y, z, MODE == kFusedBwd, lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N);
   if (!s.g.ok2) return;
   s.live = true;
   bilinear_weights(s.g, s.bw);
   if (MODE == kFusedBwd) {
     const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
-                        (long long)b * a.N * a.dist_pix_stride + (long long)h * a.dist_head_stride;
+                        ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
+    const int Dlim = min(s.g.Dd, a.D);
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      load_depth_pair(dist_bh, a.dist_pix_stride, s.g.pix[k], s.g.z0, s.g.Dd, a.D, s.g.ok3, s.lo[k],
-                      s.hi[k]);
+      load_depth_pair(dist_bh, a.dist_pix_stride, s.g.pix[k], s.g.z0, Dlim, s.g.ok3, s.lo[k], s.hi[k]);
     const float hd = 1.f - s.g.ld;
 #pragma unroll
     for (int k = 0; k < 4; ++k) s.ds[k] = s.g.ok3 ? s.lo[k] * hd + s.hi[k] * s.g.ld : 0.f;
   } else {
-    const float4 t = __ldg(reinterpret_cast<const float4 *>(a.ds_in) + pt);
+    const float4 t = __ldg(reinterpret_cast<const float4 *>(a.ds_in) + (c.pt0 + j));
     s.ds[0] = s.g.pix[0] >= 0 ? t.x : 0.f;
     s.ds[1] = s.g.pix[1] >= 0 ? t.y : 0.f;
     s.ds[2] = s.g.pix[2] >= 0 ? t.z : 0.f;
@@ -84,10 +77,10 @@ __device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, 
 
 // Everything that follows from the four dot products t[k] = <value row k, grad_out row>.
 template <typename DT, int MODE>
-__device__ __forceinline__ void bwd_point_epilogue(const KArgs &a, long long item, int j, int b, int h,
+__device__ __forceinline__ void bwd_point_epilogue(const KArgs &a, const ItemCtx &c, int j,
                                                    const PointState &s, const float (&t)[4]) {
   if (j >= a.LP) return;
-  const long long pt = item * a.LP + j;
+  const long long pt = c.pt0 + j;
   float g_attn = 0.f, g_x = 0.f, g_y = 0.f, g_z = 0.f;
   float gds[4] = {0.f, 0.f, 0.f, 0.f};
   if (s.live) {
@@ -104,20 +97,16 @@ __device__ __forceinline__ void bwd_point_epilogue(const KArgs &a, long long ite
     g_x = (float)s.g.W * s.aw * (hh * (e1 - e0) + s.g.lh * (e2 - e3));
     g_y = (float)s.g.Hh * s.aw * (hw * (e3 - e0) + s.g.lw * (e2 - e1));
     if (MODE == kFusedBwd && s.g.ok3) {
-      float *gd_bh = a.grad_dist + (long long)b * a.N * a.dist_pix_stride +
-                     (long long)h * a.dist_head_stride;
+      float *gd_bh = a.grad_dist + ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
       const float hd = 1.f - s.g.ld;
-      const bool zlo = s.g.z0 >= 0 && s.g.z0 < a.D;
-      const bool zhi = s.g.z0 + 1 <= s.g.Dd - 1 && s.g.z0 + 1 < a.D;
+      const int Dlim = min(s.g.Dd, a.D);
       float acc = 0.f;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (s.g.pix[k] >= 0) {
-          float *p = gd_bh + (long long)s.g.pix[k] * a.dist_pix_stride + s.g.z0;
-          if (gds[k] != 0.f) {
-            if (zlo) red_add(p, hd * gds[k]);
-            if (zhi) red_add(p + 1, s.g.ld * gds[k]);
-          }
+          if (gds[k] != 0.f)
+            red_depth_pair(gd_bh, a.dist_pix_stride, s.g.pix[k], s.g.z0, Dlim, a.D, hd * gds[k],
+                           s.g.ld * gds[k]);
           acc = fmaf(gds[k], s.hi[k] - s.lo[k], acc);
         }
       }
@@ -136,8 +125,12 @@ __device__ __forceinline__ void bwd_point_epilogue(const KArgs &a, long long ite
 // ------------------------------------------------------------------------------------------------
 // fused / given-depth-score backward, C a power of two with 16-byte row fragments
 // ------------------------------------------------------------------------------------------------
-template <typename VT, typename DT, int C, int MODE>
-__global__ void __launch_bounds__(kThreads)
+// fp32 value: 4 CTAs (32 warps) per SM is the measured optimum (64 registers, a few bytes of spill);
+// bf16 value carries twice the channels per lane and would spill heavily under that cap.
+template <typename VT> constexpr int backward_min_ctas() { return sizeof(VT) == 4 ? 4 : 1; }
+
+template <typename VT, typename DT, int C, int MODE, bool FULL>
+__global__ void __launch_bounds__(kThreads, backward_min_ctas<VT>())
 dfa3d_backward_kernel(const KArgs a) {
   constexpr int V = RowVec<VT>::kElems;
   constexpr int G = C / V;
@@ -145,25 +138,23 @@ dfa3d_backward_kernel(const KArgs a) {
   constexpr int U = 4;
 
   __shared__ LevelTable lv;
-  __shared__ RowEntryB rows[kWarpsPerCta][128];
+  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
   __shared__ __align__(16) float dots[kWarpsPerCta][128];
   stage_levels(lv, a);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * kWarpsPerCta + warp;
-  if (item >= a.items) return;
-  const int h = (int)(item % a.H);
-  const int b = (int)(item / ((long long)a.Q * a.H));
+  ItemCtx c;
+  if (!item_context(a, warp, c)) return;
   const int sub = lane % G, grp = lane / G;
-  const long long slice = ((long long)b * a.N * a.H + h) * C + sub * V;
+  const long long slice = ((long long)c.b * a.N * a.H + c.h) * C + sub * V;
   const VT *vbase = reinterpret_cast<const VT *>(a.value) + slice;
   float *gvbase = a.grad_value + slice;
-  RowEntryB *my = rows[warp];
-  float *myd = dots[warp];
+  const RowEntry *my = rows[warp] + grp;
+  float *myd = dots[warp] + grp;
 
   float go[V];
   {
-    const float *gp = a.grad_out + item * C + sub * V;
+    const float *gp = a.grad_out + (c.item * C + sub * V);
 #pragma unroll
     for (int i = 0; i < V; i += 4) {
       const float4 t = __ldg(reinterpret_cast<const float4 *>(gp + i));
@@ -175,18 +166,16 @@ dfa3d_backward_kernel(const KArgs a) {
     PointState st;
     float wgt[4];
     int off[4];
-    bwd_point<DT, MODE>(a, lv, item, chunk + lane, b, h, st, wgt, off);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) my[lane * 4 + k] = RowEntryB{off[k], wgt[k]};
+    bwd_point<DT, MODE>(a, lv, c, chunk + lane, st, wgt, off);
+    store_rows(rows[warp], lane, off, wgt);
     __syncwarp();
-    const int nrows = min(32, a.LP - chunk) * 4;
-    for (int r0 = 0; r0 < nrows; r0 += R * U) {
-      RowEntryB e[U];
+    auto step = [&](int r0, int nrows) {
+      RowEntry e[U];
       float v[U][V];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int r = r0 + u * R + grp;
-        e[u] = (r < nrows) ? my[r] : RowEntryB{-1, 0.f};
+        const int r = r0 + u * R;
+        e[u] = (FULL || r + grp < nrows) ? my[r] : RowEntry{-1, 0.f};
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -204,8 +193,8 @@ dfa3d_backward_kernel(const KArgs a) {
         for (int i = 0; i < V; ++i) d = fmaf(v[u][i], go[i], d);
 #pragma unroll
         for (int s = 1; s < G; s <<= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
-        const int r = r0 + u * R + grp;
-        if (sub == 0 && r < nrows) myd[r] = d;
+        const int r = r0 + u * R;
+        if (sub == 0 && (FULL || r + grp < nrows)) myd[r] = d;
         if (e[u].off >= 0 && e[u].wgt != 0.f) {
           float *gp = gvbase + e[u].off;
 #pragma unroll
@@ -214,11 +203,14 @@ dfa3d_backward_kernel(const KArgs a) {
                        e[u].wgt * go[i + 3]);
         }
       }
-    }
+    };
+    const int nrows = FULL ? 128 : min(32, a.LP - chunk) * 4;
+#pragma unroll 1
+    for (int r0 = 0; r0 < nrows; r0 += R * U) step(r0, nrows);
     __syncwarp();
-    const float4 tq = reinterpret_cast<const float4 *>(myd)[lane];
+    const float4 tq = reinterpret_cast<const float4 *>(dots[warp])[lane];
     const float t[4] = {tq.x, tq.y, tq.z, tq.w};
-    bwd_point_epilogue<DT, MODE>(a, item, chunk + lane, b, h, st, t);
+    bwd_point_epilogue<DT, MODE>(a, c, chunk + lane, st, t);
     __syncwarp();
   }
 }
@@ -230,38 +222,35 @@ template <typename VT, typename DT, int MODE>
 __global__ void __launch_bounds__(kThreads)
 dfa3d_backward_generic_kernel(const KArgs a) {
   __shared__ LevelTable lv;
-  __shared__ RowEntryB rows[kWarpsPerCta][128];
+  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
   __shared__ __align__(16) float dots[kWarpsPerCta][128];
   stage_levels(lv, a);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * kWarpsPerCta + warp;
-  if (item >= a.items) return;
+  ItemCtx c;
+  if (!item_context(a, warp, c)) return;
   const int C = a.C;
-  const int h = (int)(item % a.H);
-  const int b = (int)(item / ((long long)a.Q * a.H));
-  const long long slice = ((long long)b * a.N * a.H + h) * C;
+  const long long slice = ((long long)c.b * a.N * a.H + c.h) * C;
   const VT *vbase = reinterpret_cast<const VT *>(a.value) + slice;
   float *gvbase = a.grad_value + slice;
-  const float *gop = a.grad_out + item * C;
-  RowEntryB *my = rows[warp];
+  const float *gop = a.grad_out + c.item * C;
+  RowEntry *my = rows[warp];
   float *myd = dots[warp];
   for (int chunk = 0; chunk < a.LP; chunk += 32) {
     PointState st;
     float wgt[4];
     int off[4];
-    bwd_point<DT, MODE>(a, lv, item, chunk + lane, b, h, st, wgt, off);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) my[lane * 4 + k] = RowEntryB{off[k], wgt[k]};
+    bwd_point<DT, MODE>(a, lv, c, chunk + lane, st, wgt, off);
+    store_rows(my, lane, off, wgt);
     __syncwarp();
     const int nrows = min(32, a.LP - chunk) * 4;
     for (int r = 0; r < nrows; ++r) {
-      const RowEntryB e = my[r];
+      const RowEntry e = my[r];
       float d = 0.f;
       if (e.off >= 0) {
-        for (int c = lane; c < C; c += 32) {
-          const float g = __ldg(gop + c);
-          d = fmaf(load_scalar(vbase + e.off + c), g, d);
-          if (e.wgt != 0.f) red_add(gvbase + e.off + c, e.wgt * g);
+        for (int ch = lane; ch < C; ch += 32) {
+          const float g = __ldg(gop + ch);
+          d = fmaf(load_scalar(vbase + e.off + ch), g, d);
+          if (e.wgt != 0.f) red_add(gvbase + e.off + ch, e.wgt * g);
         }
       }
 #pragma unroll
@@ -271,7 +260,7 @@ dfa3d_backward_generic_kernel(const KArgs a) {
     __syncwarp();
     const float4 tq = reinterpret_cast<const float4 *>(myd)[lane];
     const float t[4] = {tq.x, tq.y, tq.z, tq.w};
-    bwd_point_epilogue<DT, MODE>(a, item, chunk + lane, b, h, st, t);
+    bwd_point_epilogue<DT, MODE>(a, c, chunk + lane, st, t);
     __syncwarp();
   }
 }
@@ -291,29 +280,26 @@ dfa3d_depth_score_backward_kernel(const KArgs a) {
     const int j = (int)(pt - item * a.LP);
     const int l = j / a.P;
     const int h = (int)(item % a.H);
-    const int b = (int)(item / ((long long)a.Q * a.H));
+    const int b = (int)(item / a.items_per_cam);
     const float *lp = a.loc + pt * 3;
     const PointGeo g = point_geometry(__ldg(lp), __ldg(lp + 1), __ldg(lp + 2), true, lv.h[l], lv.w[l],
                                       lv.d[l], lv.start[l], a.N);
     float g_z = 0.f;
     if (g.ok3) {
-      const long long bh = (long long)b * a.N * a.dist_pix_stride + (long long)h * a.dist_head_stride;
+      const long long bh = (long long)b * a.N * a.dist_pix_stride + h * a.dist_head_stride;
       const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) + bh;
       float *gd_bh = a.grad_dist + bh;
       const float4 gq = __ldg(reinterpret_cast<const float4 *>(a.grad_ds_in) + pt);
       const float gds[4] = {gq.x, gq.y, gq.z, gq.w};
       const float hd = 1.f - g.ld;
-      const bool zlo = g.z0 >= 0 && g.z0 < a.D;
-      const bool zhi = g.z0 + 1 <= g.Dd - 1 && g.z0 + 1 < a.D;
+      const int Dlim = min(g.Dd, a.D);
       float acc = 0.f;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (g.pix[k] >= 0) {
           float lo, hi;
-          load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, g.Dd, a.D, true, lo, hi);
-          float *p = gd_bh + (long long)g.pix[k] * a.dist_pix_stride + g.z0;
-          if (zlo) red_add(p, hd * gds[k]);
-          if (zhi) red_add(p + 1, g.ld * gds[k]);
+          load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, Dlim, true, lo, hi);
+          red_depth_pair(gd_bh, a.dist_pix_stride, g.pix[k], g.z0, Dlim, a.D, hd * gds[k], g.ld * gds[k]);
           acc = fmaf(gds[k], hi - lo, acc);
         }
       }
@@ -327,19 +313,32 @@ dfa3d_depth_score_backward_kernel(const KArgs a) {
 // ------------------------------------------------------------------------------------------------
 // host-side dispatch
 // ------------------------------------------------------------------------------------------------
-template <typename VT, typename DT, int MODE>
-static cudaError_t launch_backward_vd(const KArgs &a, cudaStream_t s) {
-  const unsigned grid = (unsigned)((a.items + kWarpsPerCta - 1) / kWarpsPerCta);
+template <typename VT, typename DT, int MODE, bool FULL>
+static void launch_backward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
   constexpr int V = RowVec<VT>::kElems;
-  const int g = (a.C % V == 0) ? a.C / V : 0;
-  switch (g) {
-    case 2:  dfa3d_backward_kernel<VT, DT, 2 * V, MODE><<<grid, kThreads, 0, s>>>(a); break;
-    case 4:  dfa3d_backward_kernel<VT, DT, 4 * V, MODE><<<grid, kThreads, 0, s>>>(a); break;
-    case 8:  dfa3d_backward_kernel<VT, DT, 8 * V, MODE><<<grid, kThreads, 0, s>>>(a); break;
-    case 16: dfa3d_backward_kernel<VT, DT, 16 * V, MODE><<<grid, kThreads, 0, s>>>(a); break;
+  switch ((a.C % V == 0) ? a.C / V : 0) {
+    case 2:  dfa3d_backward_kernel<VT, DT, 2 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    case 4:  dfa3d_backward_kernel<VT, DT, 4 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    case 8:  dfa3d_backward_kernel<VT, DT, 8 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    case 16: dfa3d_backward_kernel<VT, DT, 16 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
     default: dfa3d_backward_generic_kernel<VT, DT, MODE><<<grid, kThreads, 0, s>>>(a); break;
   }
-  return cudaGetLastError();
+}
+
+template <typename VT, typename DT, int MODE>
+static cudaError_t launch_backward_vd(const KArgs &a0, cudaStream_t s) {
+  const bool full = a0.LP % 32 == 0;
+  for (int b0 = 0; b0 < a0.B; b0 += 65535) {      // grid.y limit
+    KArgs a = a0;
+    a.b0 = b0;
+    const dim3 grid((unsigned)((a.items_per_cam + kWarpsPerCta - 1) / kWarpsPerCta),
+                    (unsigned)min(65535, a0.B - b0), 1);
+    if (full) launch_backward_g<VT, DT, MODE, true>(a, grid, s);
+    else launch_backward_g<VT, DT, MODE, false>(a, grid, s);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 cudaError_t launch_backward(const KArgs &a, bool value_bf16, bool dist_bf16, bool given_ds,

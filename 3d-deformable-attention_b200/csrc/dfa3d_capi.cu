@@ -34,6 +34,8 @@ int check_problem(const dfa3d_problem *p, bool need_value, bool need_dist) {
     return fail(DFA3D_ERR_UNSUPPORTED, "L=%d exceeds DFA3D_MAX_LEVELS=%d", p->L, DFA3D_MAX_LEVELS);
   if ((long long)p->L * p->P > (1 << 20))
     return fail(DFA3D_ERR_UNSUPPORTED, "L*P=%lld is too large", (long long)p->L * p->P);
+  if ((long long)p->Q * p->H >= (1LL << 31) - 8)
+    return fail(DFA3D_ERR_UNSUPPORTED, "Q*H must stay below 2^31");
   if (need_value) {
     if (p->C <= 0 || p->C > DFA3D_MAX_CHANNELS)
       return fail(DFA3D_ERR_UNSUPPORTED, "C=%d outside [1, %d]", p->C, DFA3D_MAX_CHANNELS);
@@ -72,8 +74,9 @@ dfa3d::KArgs base_args(const dfa3d_problem *p, int shape_stride, int loc_stride)
   a.shape_stride = shape_stride;
   a.loc_stride = loc_stride;
   a.items = (long long)p->B * p->Q * p->H;
-  a.dist_head_stride = p->dist_head_stride;
-  a.dist_pix_stride = p->dist_head_stride == 0 ? (long long)p->D : (long long)p->H * p->D;
+  a.items_per_cam = p->Q * p->H;
+  a.dist_head_stride = (int)p->dist_head_stride;
+  a.dist_pix_stride = p->dist_head_stride == 0 ? p->D : p->H * p->D;
   return a;
 }
 

@@ -43,11 +43,13 @@ struct KArgs {
   float *grad_ds_out;      // (B,Q,H,L,P,4), overwritten, or null
   int B, N, H, C, D, L, Q, P;
   int LP;                  // L*P
+  int items_per_cam;       // Q*H: one warp per (query, head) of a camera
+  int b0;                  // camera index of blockIdx.y == 0 (launches cover <= 65535 cameras each)
   int shape_stride;        // 2 or 3
   int loc_stride;          // 2 or 3
   long long items;         // B*Q*H
-  long long dist_pix_stride;   // elements between pixels of dist: H*D or D
-  long long dist_head_stride;  // D or 0
+  int dist_pix_stride;     // elements between pixels of dist: H*D or D
+  int dist_head_stride;    // D or 0
 };
 
 // Level table staged in shared memory once per CTA.
@@ -63,6 +65,30 @@ __device__ __forceinline__ void stage_levels(LevelTable &t, const KArgs &a) {
     t.start[l] = (int)a.lsi[l];
   }
   __syncthreads();
+}
+
+// What a warp knows about its (camera b, query q, head h) item: 64-bit bases computed once, so that
+// the per-point and per-row arithmetic stays 32-bit.
+struct ItemCtx {
+  int b, h;
+  long long item;           // (b*Q + q)*H + h
+  const float *loc;         // first location of the item
+  const float *attn;        // first attention weight of the item
+  long long pt0;            // index of the item's first point: item * LP
+};
+
+// blockIdx.y (+ b0) selects the camera, blockIdx.x * warps + warp the (query, head) pair inside it.
+// Returns false for the warps past the end of the camera.
+__device__ __forceinline__ bool item_context(const KArgs &a, int warp, ItemCtx &c) {
+  const unsigned idx = blockIdx.x * kWarpsPerCta + warp;
+  if (idx >= (unsigned)a.items_per_cam) return false;
+  c.b = (int)blockIdx.y + a.b0;
+  c.h = (int)(idx % (unsigned)a.H);
+  c.item = (long long)c.b * a.items_per_cam + idx;
+  c.pt0 = c.item * a.LP;
+  c.loc = a.loc + c.pt0 * a.loc_stride;
+  c.attn = a.attn + c.pt0;
+  return true;
 }
 
 // Geometry of one sampling point.
@@ -115,16 +141,35 @@ __device__ __forceinline__ float load_scalar(const __nv_bfloat16 *p) {
   return __bfloat162float(__ldg(p));
 }
 
-// The two depth bins of corner k (0 where the bin is outside [0, D-1] or the corner is unusable).
+// One gathered row: where it starts and what it is multiplied by.
+struct __align__(8) RowEntry {
+  int off;    // element offset of the row inside the (b, h) slice of value; -1 = skip
+  float wgt;  // attention * bilinear * depth score
+};
+
+// A warp's table of 32 points x 4 corners: entry (p, k) in slot p*4 + k.  (Swizzling the two 16-byte
+// halves of a lane's store to avoid its 2-way bank conflict was measured: the extra index arithmetic
+// in the readers cost more than the conflicts.)
+__device__ __forceinline__ void store_rows(RowEntry *table, int lane, const int (&off)[4],
+                                           const float (&wgt)[4]) {
+  uint4 *dst = reinterpret_cast<uint4 *>(table) + lane * 2;
+  dst[0] = make_uint4((uint32_t)off[0], __float_as_uint(wgt[0]), (uint32_t)off[1], __float_as_uint(wgt[1]));
+  dst[1] = make_uint4((uint32_t)off[2], __float_as_uint(wgt[2]), (uint32_t)off[3], __float_as_uint(wgt[3]));
+}
+
+// The two depth bins z0, z0+1 of one corner pixel (0 where a bin is outside [0, Dlim-1] or the corner
+// is unusable).  Dlim = min(depth size of the level, channel count of dist).  Two scalar loads: the
+// second one hits the sector the first one brought into L1.  (One aligned 16-byte window load per
+// pair was measured slower: the forward is issue-bound and the element extraction costs more
+// instructions than the second load.)
 template <typename DT>
-__device__ __forceinline__ void load_depth_pair(const DT *dist_bh, long long pix_stride, int pix,
-                                                int z0, int Dd, int Dchan, bool ok3, float &lo,
-                                                float &hi) {
+__device__ __forceinline__ void load_depth_pair(const DT *dist_bh, int pix_stride, int pix, int z0,
+                                                int Dlim, bool ok3, float &lo, float &hi) {
   lo = 0.f; hi = 0.f;
   if (ok3 && pix >= 0) {
-    const DT *p = dist_bh + (long long)pix * pix_stride;
-    if (z0 >= 0 && z0 < Dchan) lo = load_scalar(p + z0);
-    if (z0 + 1 <= Dd - 1 && z0 + 1 < Dchan) hi = load_scalar(p + z0 + 1);
+    const DT *p = dist_bh + ((long long)pix * pix_stride + z0);
+    if (z0 >= 0 && z0 < Dlim) lo = load_scalar(p);
+    if (z0 + 1 < Dlim) hi = load_scalar(p + 1);
   }
 }
 
@@ -158,6 +203,35 @@ __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float 
 }
 __device__ __forceinline__ void red_add(float *addr, float a) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
+}
+__device__ __forceinline__ void red_add_v2(float *addr, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+
+// grad_dist[pix, z0] += a_lo ; grad_dist[pix, z0+1] += a_hi  (each only if the bin is inside
+// [0, Dlim-1]).  The pair is adjacent, so it goes out as one 8-byte vector reduction when it is 8-byte
+// aligned, as one 16-byte reduction padded with zeros when it sits in the middle of an aligned 16-byte
+// block that lies wholly inside the pixel's row, and as two scalars otherwise: 1.25 L2 reduction
+// packets per corner on average where two scalars were 2.
+__device__ __forceinline__ void red_depth_pair(float *gd_bh, int pix_stride, int pix, int z0, int Dlim,
+                                               int Dchan, float a_lo, float a_hi) {
+  const bool vlo = z0 >= 0 && z0 < Dlim, vhi = z0 + 1 >= 0 && z0 + 1 < Dlim;
+  float *p = gd_bh + ((long long)pix * pix_stride + z0);
+  if (vlo && vhi) {
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(p);
+    if ((addr & 7) == 0) {
+      red_add_v2(p, a_lo, a_hi);
+    } else if ((addr & 15) == 4 && z0 >= 1 && z0 + 2 < Dchan) {
+      red_add_v4(p - 1, 0.f, a_lo, a_hi, 0.f);
+    } else {
+      red_add(p, a_lo);
+      red_add(p + 1, a_hi);
+    }
+  } else if (vlo) {
+    red_add(p, a_lo);
+  } else if (vhi) {
+    red_add(p + 1, a_hi);
+  }
 }
 
 }  // namespace dfa3d

@@ -13,6 +13,10 @@
 // This replaces the reference's pair of kernels (one thread per (b,q,h) for the depth scores,
 // ms_depth_score_sample_cuda_kernel.cuh:94-148; one thread per output channel for the attention,
 // wms_deform_attn_cuda_kernel.cuh:240-303) and the depth_score round trip through HBM between them.
+//
+// The kernels are issue-bound as much as memory-bound (ncu: issue slots 2/3 busy), so index
+// arithmetic is kept 32-bit: the grid's y dimension is the camera, 64-bit bases are formed once per
+// warp, and when L*P is a multiple of 32 (FULL) the row loop has a compile-time trip count.
 #include "dfa3d_common.cuh"
 #include "dfa3d_launch.h"
 
@@ -20,43 +24,37 @@ namespace dfa3d {
 
 enum FwdMode { kFused = 0, kGivenDepthScore = 1 };
 
-struct __align__(8) RowEntry {
-  int off;    // element offset of the row inside the (b, h) slice of value; -1 = skip
-  float wgt;  // attention * bilinear * depth score
-};
-
 // ------------------------------------------------------------------------------------------------
-// prologue shared by forward and backward: per-lane point -> 4 row entries (+ depth scores)
+// prologue: per-lane point -> 4 row entries (+ depth scores)
 // ------------------------------------------------------------------------------------------------
 template <typename DT, int MODE>
-__device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, long long item, int j,
-                                          int b, int h, float (&ds)[4], float (&wgt)[4],
-                                          int (&off)[4]) {
+__device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, const ItemCtx &c, int j,
+                                          float (&ds)[4], float (&wgt)[4], int (&off)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) { ds[k] = 0.f; wgt[k] = 0.f; off[k] = -1; }
   if (j >= a.LP) return;
   const int l = j / a.P;
-  const long long pt = item * a.LP + j;
-  const float *lp = a.loc + pt * a.loc_stride;
+  const float *lp = c.loc + j * a.loc_stride;
   const float x = __ldg(lp), y = __ldg(lp + 1);
   const float z = (MODE == kFused) ? __ldg(lp + 2) : 0.f;
-  const float aw = __ldg(a.attn + pt);
+  const float aw = __ldg(c.attn + j);
   const PointGeo g = point_geometry(x, y, z, MODE == kFused, lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N);
   if (!g.ok2) return;
   float bw[4];
   bilinear_weights(g, bw);
   if (MODE == kFused) {
     const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
-                        (long long)b * a.N * a.dist_pix_stride + (long long)h * a.dist_head_stride;
+                        ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
     float lo[4], hi[4];
+    const int Dlim = min(g.Dd, a.D);
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, g.Dd, a.D, g.ok3, lo[k], hi[k]);
+      load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, Dlim, g.ok3, lo[k], hi[k]);
     const float hd = 1.f - g.ld;
 #pragma unroll
     for (int k = 0; k < 4; ++k) ds[k] = g.ok3 ? lo[k] * hd + hi[k] * g.ld : 0.f;
   } else {
-    const float4 t = __ldg(reinterpret_cast<const float4 *>(a.ds_in) + pt);
+    const float4 t = __ldg(reinterpret_cast<const float4 *>(a.ds_in) + (c.pt0 + j));
     ds[0] = g.pix[0] >= 0 ? t.x : 0.f;
     ds[1] = g.pix[1] >= 0 ? t.y : 0.f;
     ds[2] = g.pix[2] >= 0 ? t.z : 0.f;
@@ -65,18 +63,21 @@ __device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, 
   const int row = a.H * a.C;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    if (g.pix[k] >= 0) {
+    const float w = aw * (bw[k] * ds[k]);
+    if (g.pix[k] >= 0 && w != 0.f) {     // rows that would add nothing are not fetched
       off[k] = g.pix[k] * row;
-      wgt[k] = aw * (bw[k] * ds[k]);
+      wgt[k] = w;
     }
   }
 }
 
 // ------------------------------------------------------------------------------------------------
-// fused / given-depth-score forward, C a power of two with 16-byte row fragments
+// fused / given-depth-score forward, C/V a power of two (V = elements per 16-byte fragment)
 // ------------------------------------------------------------------------------------------------
-template <typename VT, typename DT, int C, int MODE, bool WRITE_DS>
-__global__ void __launch_bounds__(kThreads)
+// 5 CTAs (40 warps) per SM: measured best; at 6+ the register cap starts to cost more than the
+// extra warps hide.
+template <typename VT, typename DT, int C, int MODE, bool WRITE_DS, bool FULL>
+__global__ void __launch_bounds__(kThreads, 5)
 dfa3d_forward_kernel(const KArgs a) {
   constexpr int V = RowVec<VT>::kElems;   // elements per 16-byte fragment
   constexpr int G = C / V;                // lanes per row
@@ -85,18 +86,15 @@ dfa3d_forward_kernel(const KArgs a) {
   static_assert(G >= 1 && G <= 32 && (G & (G - 1)) == 0, "C/V must be a power of two <= 32");
 
   __shared__ LevelTable lv;
-  __shared__ RowEntry rows[kWarpsPerCta][128];
+  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
   stage_levels(lv, a);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * kWarpsPerCta + warp;
-  if (item >= a.items) return;
-  const int h = (int)(item % a.H);
-  const int b = (int)(item / ((long long)a.Q * a.H));
-  const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)b * a.N * a.H + h) * C +
-                    (lane % G) * V;
-  const int grp = lane / G;
-  RowEntry *my = rows[warp];
+  ItemCtx c;
+  if (!item_context(a, warp, c)) return;
+  const VT *vbase = reinterpret_cast<const VT *>(a.value) + (((long long)c.b * a.N * a.H + c.h) * C +
+                                                             (lane % G) * V);
+  const RowEntry *my = rows[warp] + lane / G;
 
   float acc[V];
 #pragma unroll
@@ -105,22 +103,19 @@ dfa3d_forward_kernel(const KArgs a) {
   for (int chunk = 0; chunk < a.LP; chunk += 32) {
     float ds[4], wgt[4];
     int off[4];
-    fwd_point<DT, MODE>(a, lv, item, chunk + lane, b, h, ds, wgt, off);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) my[lane * 4 + k] = RowEntry{off[k], wgt[k]};
+    fwd_point<DT, MODE>(a, lv, c, chunk + lane, ds, wgt, off);
+    store_rows(rows[warp], lane, off, wgt);
     if (WRITE_DS && chunk + lane < a.LP)
-      reinterpret_cast<float4 *>(a.ds_out)[item * a.LP + chunk + lane] =
-          make_float4(ds[0], ds[1], ds[2], ds[3]);
+      reinterpret_cast<float4 *>(a.ds_out)[c.pt0 + chunk + lane] = make_float4(ds[0], ds[1], ds[2], ds[3]);
     __syncwarp();
-    const int nrows = min(32, a.LP - chunk) * 4;
-    for (int r0 = 0; r0 < nrows; r0 += R * U) {
+    // R*U rows per step: U independent 16-byte loads in flight per lane, then U fused multiply-adds.
+    auto step = [&](int r0, int nrows) {
       RowEntry e[U];
       float v[U][V];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int r = r0 + u * R + grp;
-        e[u] = (r < nrows) ? my[r] : RowEntry{-1, 0.f};
-        if (e[u].wgt == 0.f) e[u].off = -1;   // nothing to add: skip the fetch
+        const int r = r0 + u * R;
+        e[u] = (FULL || r + lane / G < nrows) ? my[r] : RowEntry{-1, 0.f};
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -135,6 +130,14 @@ dfa3d_forward_kernel(const KArgs a) {
       for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = fmaf(e[u].wgt, v[u][i], acc[i]);
+    };
+    if (FULL) {          // 128 rows: compile-time trip count, table offsets become immediates
+#pragma unroll
+      for (int r0 = 0; r0 < 128; r0 += R * U) step(r0, 128);
+    } else {
+      const int nrows = min(32, a.LP - chunk) * 4;
+#pragma unroll 1
+      for (int r0 = 0; r0 < nrows; r0 += R * U) step(r0, nrows);
     }
     __syncwarp();
   }
@@ -143,7 +146,7 @@ dfa3d_forward_kernel(const KArgs a) {
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], s);
   if (lane < G) {
-    float *o = a.out + item * C + lane * V;
+    float *o = a.out + (c.item * C + lane * V);
 #pragma unroll
     for (int i = 0; i < V; i += 4)
       *reinterpret_cast<float4 *>(o + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
@@ -157,38 +160,35 @@ template <typename VT, typename DT, int MODE, bool WRITE_DS>
 __global__ void __launch_bounds__(kThreads)
 dfa3d_forward_generic_kernel(const KArgs a) {
   __shared__ LevelTable lv;
-  __shared__ RowEntry rows[kWarpsPerCta][128];
+  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
   stage_levels(lv, a);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * kWarpsPerCta + warp;
-  if (item >= a.items) return;
+  ItemCtx c;
+  if (!item_context(a, warp, c)) return;
   const int C = a.C;
-  const int h = (int)(item % a.H);
-  const int b = (int)(item / ((long long)a.Q * a.H));
-  const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)b * a.N * a.H + h) * C;
+  const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)c.b * a.N * a.H + c.h) * C;
   RowEntry *my = rows[warp];
   for (int c0 = 0; c0 < C; c0 += 32) {          // C <= 1024: at most 32 passes
-    const int c = c0 + lane;
+    const int ch = c0 + lane;
     float acc = 0.f;
     for (int chunk = 0; chunk < a.LP; chunk += 32) {
       float ds[4], wgt[4];
       int off[4];
-      fwd_point<DT, MODE>(a, lv, item, chunk + lane, b, h, ds, wgt, off);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) my[lane * 4 + k] = RowEntry{off[k], wgt[k]};
+      fwd_point<DT, MODE>(a, lv, c, chunk + lane, ds, wgt, off);
+      store_rows(my, lane, off, wgt);
       if (WRITE_DS && c0 == 0 && chunk + lane < a.LP)
-        reinterpret_cast<float4 *>(a.ds_out)[item * a.LP + chunk + lane] =
+        reinterpret_cast<float4 *>(a.ds_out)[c.pt0 + chunk + lane] =
             make_float4(ds[0], ds[1], ds[2], ds[3]);
       __syncwarp();
       const int nrows = min(32, a.LP - chunk) * 4;
-      if (c < C)
+      if (ch < C)
         for (int r = 0; r < nrows; ++r) {
           const RowEntry e = my[r];
-          if (e.off >= 0 && e.wgt != 0.f) acc = fmaf(e.wgt, load_scalar(vbase + e.off + c), acc);
+          if (e.off >= 0) acc = fmaf(e.wgt, load_scalar(vbase + e.off + ch), acc);
         }
       __syncwarp();
     }
-    if (c < C) a.out[item * C + c] = acc;
+    if (ch < C) a.out[c.item * C + ch] = acc;
   }
 }
 
@@ -207,18 +207,19 @@ dfa3d_depth_score_forward_kernel(const KArgs a) {
     const int j = (int)(pt - item * a.LP);
     const int l = j / a.P;
     const int h = (int)(item % a.H);
-    const int b = (int)(item / ((long long)a.Q * a.H));
+    const int b = (int)(item / a.items_per_cam);
     const float *lp = a.loc + pt * 3;
     const PointGeo g = point_geometry(__ldg(lp), __ldg(lp + 1), __ldg(lp + 2), true, lv.h[l], lv.w[l],
                                       lv.d[l], lv.start[l], a.N);
     const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
-                        (long long)b * a.N * a.dist_pix_stride + (long long)h * a.dist_head_stride;
+                        ((long long)b * a.N * a.dist_pix_stride + h * a.dist_head_stride);
     float ds[4];
     const float hd = 1.f - g.ld;
+    const int Dlim = min(g.Dd, a.D);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float lo, hi;
-      load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, g.Dd, a.D, g.ok3, lo, hi);
+      load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, Dlim, g.ok3, lo, hi);
       ds[k] = g.ok3 ? lo * hd + hi * g.ld : 0.f;
     }
     reinterpret_cast<float4 *>(a.ds_out)[pt] = make_float4(ds[0], ds[1], ds[2], ds[3]);
@@ -228,36 +229,40 @@ dfa3d_depth_score_forward_kernel(const KArgs a) {
 // ------------------------------------------------------------------------------------------------
 // host-side dispatch
 // ------------------------------------------------------------------------------------------------
-template <typename VT, typename DT, int MODE, bool WRITE_DS>
-static cudaError_t launch_forward_c(const KArgs &a, cudaStream_t s) {
-  const unsigned grid = (unsigned)((a.items + kWarpsPerCta - 1) / kWarpsPerCta);
-  constexpr int V = RowVec<VT>::kElems;
-  switch (a.C / V) {
-    case 2:  dfa3d_forward_kernel<VT, DT, 2 * V, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
-    case 4:  dfa3d_forward_kernel<VT, DT, 4 * V, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
-    case 8:  dfa3d_forward_kernel<VT, DT, 8 * V, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
-    case 16: dfa3d_forward_kernel<VT, DT, 16 * V, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
-    default: dfa3d_forward_generic_kernel<VT, DT, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
-  }
-  return cudaGetLastError();
+static dim3 item_grid(const KArgs &a, int cams) {
+  return dim3((unsigned)((a.items_per_cam + kWarpsPerCta - 1) / kWarpsPerCta), (unsigned)cams, 1);
 }
 
-static bool vector_path_ok(const KArgs &a, int V) {
-  const int g = a.C / V;
-  return a.C % V == 0 && (g == 2 || g == 4 || g == 8 || g == 16);
+template <typename VT, typename DT, int MODE, bool WRITE_DS, bool FULL>
+static void launch_forward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
+  constexpr int V = RowVec<VT>::kElems;
+  switch ((a.C % V == 0) ? a.C / V : 0) {
+    case 2:  dfa3d_forward_kernel<VT, DT, 2 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    case 4:  dfa3d_forward_kernel<VT, DT, 4 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    case 8:  dfa3d_forward_kernel<VT, DT, 8 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    case 16: dfa3d_forward_kernel<VT, DT, 16 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    default: dfa3d_forward_generic_kernel<VT, DT, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
+  }
 }
 
 template <typename VT, typename DT, int MODE>
-static cudaError_t launch_forward_vd(const KArgs &a, cudaStream_t s) {
-  const bool gen = !vector_path_ok(a, RowVec<VT>::kElems);
-  const unsigned grid = (unsigned)((a.items + kWarpsPerCta - 1) / kWarpsPerCta);
-  if (gen) {
-    if (a.ds_out) dfa3d_forward_generic_kernel<VT, DT, MODE, true><<<grid, kThreads, 0, s>>>(a);
-    else dfa3d_forward_generic_kernel<VT, DT, MODE, false><<<grid, kThreads, 0, s>>>(a);
-    return cudaGetLastError();
+static cudaError_t launch_forward_vd(const KArgs &a0, cudaStream_t s) {
+  const bool full = a0.LP % 32 == 0;
+  for (int b0 = 0; b0 < a0.B; b0 += 65535) {      // grid.y limit
+    KArgs a = a0;
+    a.b0 = b0;
+    const dim3 grid = item_grid(a, min(65535, a0.B - b0));
+    if (a.ds_out) {
+      if (full) launch_forward_g<VT, DT, MODE, true, true>(a, grid, s);
+      else launch_forward_g<VT, DT, MODE, true, false>(a, grid, s);
+    } else {
+      if (full) launch_forward_g<VT, DT, MODE, false, true>(a, grid, s);
+      else launch_forward_g<VT, DT, MODE, false, false>(a, grid, s);
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
   }
-  return a.ds_out ? launch_forward_c<VT, DT, MODE, true>(a, s)
-                  : launch_forward_c<VT, DT, MODE, false>(a, s);
+  return cudaSuccess;
 }
 
 cudaError_t launch_forward(const KArgs &a, bool value_bf16, bool dist_bf16, bool given_ds,

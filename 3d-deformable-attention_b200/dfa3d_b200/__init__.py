@@ -6,6 +6,7 @@ this package is the PyTorch-facing host side: ``ext`` mirrors the reference's ex
 operators raise.
 """
 from . import _lib, ext  # noqa: F401
+from .host import HostPipeline  # noqa: F401
 from .functions import (  # noqa: F401
     MultiScale3DDeformableAttnFunction,
     MultiScale3DDeformableAttnFunction_fp32,
@@ -16,7 +17,7 @@ from .functions import (  # noqa: F401
 )
 
 __all__ = [
-    "ext",
+    "ext", "HostPipeline",
     "MultiScaleDepthScoreSampleFunction", "WeightedMultiScaleDeformableAttnFunction",
     "MultiScale3DDeformableAttnFunction",
     "MultiScaleDepthScoreSampleFunction_fp32", "WeightedMultiScaleDeformableAttnFunction_fp32",

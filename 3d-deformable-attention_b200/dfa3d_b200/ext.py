@@ -199,14 +199,22 @@ def _fused_problem(value, dist, shapes3, lsi, loc3, attn):
 
 
 def dfa3d_fused_forward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
-                        sampling_locations, attention_weights, im2col_step, need_depth_score=True):
-    """Returns (output (B,Q,H*C), depth_score (B,Q,H,L,P,4) or None)."""
+                        sampling_locations, attention_weights, im2col_step, need_depth_score=True,
+                        out=None):
+    """Returns (output (B,Q,H*C), depth_score (B,Q,H,L,P,4) or None).  `out`, if given, is a
+    preallocated float32 (B,Q,H*C) tensor that receives the output (every element is written)."""
     pr, (B, Q, H, L, P, C) = _fused_problem(value, value_dpt_dist, value_spatial_shapes,
                                             value_level_start_index, sampling_locations,
                                             attention_weights)
     _step_check(B, im2col_step)
     dev = value.device
-    out = torch.empty((B, Q, H * C), dtype=torch.float32, device=dev)
+    if out is None:
+        out = torch.empty((B, Q, H * C), dtype=torch.float32, device=dev)
+    else:
+        _chk(out, "out", _F32)
+        _same_device(value, out)
+        if out.numel() != B * Q * H * C:
+            raise RuntimeError("out has the wrong number of elements")
     ds = torch.empty((B, Q, H, L, P, 4), dtype=torch.float32, device=dev) if need_depth_score else None
     with torch.cuda.device(dev):
         _lib.call("dfa3d_fused_forward", pr, _ptr(value), _ptr(value_dpt_dist),

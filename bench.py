@@ -165,21 +165,12 @@ class OursRunner:
                                       t["grad_out"], self.gv, self.gd, self.gl, self.ga, 64)
 
     def e2e_step(self, host, pinned_out):
-        """Public autograd API from pinned host buffers: H2D of every input, forward, backward, D2H of
-        the output and of all four gradients."""
-        import dfa3d_b200 as M
-        dev = self.t["loc"].device
-        value = host["value"].to(dev, non_blocking=True).requires_grad_(True)
-        dist = host["dist"].to(dev, non_blocking=True).requires_grad_(True)
-        loc = host["loc"].to(dev, non_blocking=True).requires_grad_(True)
-        attn = host["attn"].to(dev, non_blocking=True).requires_grad_(True)
-        go = host["grad_out"].to(dev, non_blocking=True)
-        out, _ = M.MultiScale3DDeformableAttnFunction.apply(value, dist, self.t["shapes"], self.t["lsi"],
-                                                            loc, attn, 64, False)
-        out.backward(go)
-        for k, g in (("out", out.detach()), ("grad_value", value.grad), ("grad_dist", dist.grad),
-                     ("grad_loc", loc.grad), ("grad_attn", attn.grad)):
-            pinned_out[k].copy_(g, non_blocking=True)
+        """Public host-buffer API (dfa3d_b200.HostPipeline): every input is copied host->device, the
+        output and all four gradients device->host, per camera, overlapped with the kernels."""
+        if getattr(self, "pipe", None) is None:
+            from dfa3d_b200 import HostPipeline
+            self.pipe = HostPipeline(self.t["shapes"], self.t["lsi"], self.t["loc"].device)
+        self.pipe.run(host, pinned_out)
 
 
 class ReferenceRunner:

@@ -282,3 +282,33 @@ def test_non_default_stream_and_inconsistent_level_table(M):
     out, _ = ext.dfa3d_fused_forward(d["value"], d["dist"], bad, d["lsi"], d["loc"], d["attn"], 64)
     torch.cuda.synchronize()
     assert torch.isfinite(out).all()
+
+
+def test_host_pipeline_matches_device_path(M):
+    """Pinned host buffers streamed per camera give the same numbers as the device-resident calls."""
+    from dfa3d_b200 import ext, HostPipeline
+    w = wl.WORKLOADS["odd"].with_(B=5)
+    d = wl.make_inputs(w)
+    t = {k: v.to(DEV) for k, v in d.items()}
+    out, _ = ext.dfa3d_fused_forward(t["value"], t["dist"], t["shapes"], t["lsi"], t["loc"], t["attn"], 64,
+                                     need_depth_score=False)
+    gv = torch.zeros_like(t["value"]); gd = torch.zeros_like(t["dist"])
+    gl = torch.empty_like(t["loc"]); ga = torch.empty_like(t["attn"])
+    ext.dfa3d_fused_backward(t["value"], t["dist"], t["shapes"], t["lsi"], t["loc"], t["attn"],
+                             t["grad_out"], gv, gd, gl, ga, 64)
+    host_in = {k: d[k].pin_memory() for k in ("value", "dist", "loc", "attn", "grad_out")}
+    host_out = {"out": torch.empty_like(d["grad_out"]).pin_memory(),
+                "grad_value": torch.empty_like(d["value"]).pin_memory(),
+                "grad_dist": torch.empty_like(d["dist"]).pin_memory(),
+                "grad_loc": torch.empty_like(d["loc"]).pin_memory(),
+                "grad_attn": torch.empty_like(d["attn"]).pin_memory()}
+    pipe = HostPipeline(d["shapes"], d["lsi"], DEV, cameras_per_chunk=2, slots=2)
+    for _ in range(2):                       # second run reuses the slots
+        pipe.run(host_in, host_out)
+        torch.cuda.synchronize()
+        assert torch.equal(host_out["out"], out.cpu())
+        assert torch.equal(host_out["grad_loc"], gl.cpu()) and torch.equal(host_out["grad_attn"], ga.cpu())
+        assert_close("grad_value", host_out["grad_value"], gv, **BWD)     # atomics: order may differ
+        assert_close("grad_dist", host_out["grad_dist"], gd, **BWD)
+    with pytest.raises(RuntimeError, match="pinned"):
+        pipe.run({k: v.clone() for k, v in d.items()}, host_out)
