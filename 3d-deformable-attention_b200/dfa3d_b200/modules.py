@@ -44,8 +44,11 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
     """3-D deformable attention over multi-level camera features and their depth distributions."""
 
     def __init__(self, embed_dims=256, num_heads=8, num_levels=4, num_points=8, im2col_step=64,
-                 batch_first=True):
+                 batch_first=True, compute_weight_update=True):
         super().__init__()
+        # weight_update (:579) needs the (B,Q,H,L,P,4) depth_score tensor written out; callers that do
+        # not use it (SpatialCrossAttention_DFA3D with use_empty=False) can switch it off
+        self.compute_weight_update = compute_weight_update
         if embed_dims % num_heads != 0:
             raise ValueError(f"embed_dims must be divisible by num_heads, but got {embed_dims} and "
                              f"{num_heads}")
@@ -102,11 +105,17 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
                              f"{reference_points.shape[-1]} instead.")
         loc = assemble_sampling_locations(reference_points, off_uv, off_d, spatial_shapes, D)
         shapes3 = torch.cat([spatial_shapes, torch.full_like(spatial_shapes[:, :1], D)], -1).contiguous()
-        output, depth_score = MultiScale3DDeformableAttnFunction_fp32.apply(
-            value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
-            loc.contiguous(), attn.contiguous(), self.im2col_step)
-        # mean depth score of a point's four corners, weighted by the attention (:579)
-        weight_update = (depth_score.mean(-1) * attn).flatten(-2).sum(-1, keepdim=True)
+        if self.compute_weight_update:
+            output, depth_score = MultiScale3DDeformableAttnFunction_fp32.apply(
+                value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
+                loc.contiguous(), attn.contiguous(), self.im2col_step)
+            # mean depth score of a point's four corners, weighted by the attention (:579)
+            weight_update = (depth_score.mean(-1) * attn).flatten(-2).sum(-1, keepdim=True)
+        else:
+            output, _ = MultiScale3DDeformableAttnFunction_fp32.apply(
+                value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
+                loc.contiguous(), attn.contiguous(), self.im2col_step, False)
+            weight_update = None
         if not self.batch_first:
             output = output.permute(1, 0, 2)
         return output, weight_update
@@ -121,6 +130,8 @@ class SpatialCrossAttention_DFA3D(nn.Module):
         self.embed_dims, self.num_cams = embed_dims, num_cams
         self.bev_h, self.bev_w, self.num_head, self.use_empty = bev_h, bev_w, num_head, use_empty
         self.deformable_attention = deformable_attention or MSDeformableAttention3D_DFA3D(embed_dims)
+        if not use_empty:
+            self.deformable_attention.compute_weight_update = False
         self.output_proj = nn.Linear(embed_dims, embed_dims)
         self.dropout = nn.Dropout(dropout)
         if use_empty:

@@ -215,6 +215,85 @@ class ReferenceRunner:
 
 
 # ----------------------------------------------------------------------------------------------
+def run_encoder_stack(a, rank, world, local):
+    """--workload cfg4: training step (forward, backward, gradient all-reduce, optimizer step) of the
+    6-layer spatial-cross-attention encoder stack on one frame (6 cameras) per GPU: 200x200 BEV queries,
+    each camera sees 10 000 of them, BEVFormer-base level shapes, 118 depth bins, 256-d, FFN 512.
+    Data parallel over frames with NCCL all-reduce of the projection-layer gradients (torch DDP)."""
+    from dfa3d_b200 import modules, workloads as wl
+    w = wl.WORKLOADS["cfg4op"]
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist_.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(0)                                   # identical initial weights on every rank
+    layers, E, cams, Z, bev = 6, w.H * w.C, 6, 4, 200 * 200
+    stack = modules.SCAEncoderStack(num_layers=layers, embed_dims=E, ffn_dims=512, num_cams=cams,
+                                    num_heads=w.H, num_levels=w.L, num_points=w.P, dropout=0.1).to(dev)
+    model = stack
+    if world > 1:
+        model = torch.nn.parallel.DistributedDataParallel(stack, device_ids=[local],
+                                                          broadcast_buffers=False)
+    opt = torch.optim.AdamW(stack.parameters(), lr=2e-4, weight_decay=0.01)
+    g = torch.Generator().manual_seed(w.seed + 1000 * rank)
+    shapes, lsi = wl.level_tensors(w)
+    mask = torch.zeros(cams, 1, bev, Z, dtype=torch.bool)
+    for c in range(cams):                                  # each camera sees w.Q of the BEV queries
+        mask[c, 0, torch.randperm(bev, generator=g)[:w.Q]] = True
+    ref = torch.rand(cams, 1, bev, Z, 3, generator=g)
+    ref[..., :2] = ref[..., :2] * 1.0846 - 0.0423
+    kw = dict(key=None,
+              value=torch.randn(cams, w.N, 1, E, generator=g).to(dev),
+              value_dpt_dist=torch.randn(cams, w.N, 1, w.D, generator=g).softmax(-1).to(dev),
+              reference_points_cam=ref.to(dev), bev_mask=mask.to(dev),
+              spatial_shapes=shapes[:, :2].contiguous().to(dev), level_start_index=lsi.to(dev))
+    query = torch.randn(1, bev, E, generator=g).to(dev)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = model(query, **kw).float().pow(2).mean()
+        loss.backward()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist_.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(a.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    tm = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist_.all_reduce(tm, op=dist_.ReduceOp.MAX)
+    ms = float(tm.item()) / a.steps
+    assert torch.isfinite(loss)
+    if rank == 0:
+        pts = w.points * layers * world
+        print(json.dumps({
+            "metric": "DFA3D fwd+bwd sampled points/s (encoder-stack training step)",
+            "value": pts / (ms * 1e-3), "unit": "sampled points/s", "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "cfg4", "layers": layers, "frames_per_gpu": 1, "cameras": cams,
+                       "bev_queries": bev, "queries_per_camera": w.Q, "depth_bins": w.D,
+                       "embed_dims": E, "ffn_dims": 512,
+                       "parallelism": f"dp{world}: NCCL all-reduce of projection gradients (DDP)"},
+            "clocks": clocks, "gpu_launches": 2 * layers * a.steps, "loss": float(loss)}), flush=True)
+    if world > 1:
+        dist_.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -235,6 +314,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", 0))
     if world != a.gpus:
         log(f"note: --gpus {a.gpus} but WORLD_SIZE={world}; using WORLD_SIZE")
+    if a.workload == "cfg4":
+        return run_encoder_stack(a, rank, world, local)
     w = wl.WORKLOADS[a.workload]
     if a.cameras > 0:
         w = w.with_(B=a.cameras)

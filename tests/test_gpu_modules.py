@@ -14,7 +14,7 @@ class _GridSampleOp:
     """Stand-in with the Function's call signature, built from differentiable torch ops."""
 
     @staticmethod
-    def apply(value, dist, shapes3, lsi, loc, attn, im2col_step):
+    def apply(value, dist, shapes3, lsi, loc, attn, im2col_step, return_depth_score=True):
         H = value.shape[2]
         dist_h = dist[:, :, None, :].expand(-1, -1, H, -1)
         out = G.dfa3d_grid_sample(value.double(), dist_h.double(), shapes3.tolist(), lsi.tolist(),
