@@ -38,7 +38,7 @@ import torch.distributed as dist_  # noqa: E402
 NCU_DRAM_TRAFFIC = {
     # profiles/dfa3d_forward_backward_cfg2_2cameras_ncu_full.md: 2-camera capture x 3 (cameras are
     # independent, traffic grows in proportion)
-    "cfg2": {"forward": 3 * (164.162560e6 + 18.415104e6), "backward": 3 * (389.944576e6 + 198.461696e6)},
+    "cfg2": {"forward": 3 * (164.730880e6 + 16.864256e6), "backward": 3 * (407.432448e6 + 211.970048e6)},
 }
 
 
