@@ -226,6 +226,10 @@ def run_encoder_stack(a, rank, world, local):
     dev = torch.device("cuda", local)
     if world > 1:
         dist_.init_process_group("nccl", device_id=dev)
+    # projection GEMMs on the TF32 tensor cores, which is what the reference's stack (PyTorch 1.9,
+    # where TF32 matmuls were on by default) ran them on; the DFA3D kernels themselves stay fp32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
     torch.manual_seed(0)                                   # identical initial weights on every rank
     layers, E, cams, Z, bev = 6, w.H * w.C, 6, 4, 200 * 200
     stack = modules.SCAEncoderStack(num_layers=layers, embed_dims=E, ffn_dims=512, num_cams=cams,
@@ -284,7 +288,7 @@ def run_encoder_stack(a, rank, world, local):
             "metric": "DFA3D fwd+bwd sampled points/s (encoder-stack training step)",
             "value": pts / (ms * 1e-3), "unit": "sampled points/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": "f32 (projection GEMMs tf32)", "data": "synthetic",
             "config": {"workload": "cfg4", "layers": layers, "frames_per_gpu": 1, "cameras": cams,
                        "bev_queries": bev, "queries_per_camera": w.Q, "depth_bins": w.D,
                        "embed_dims": E, "ffn_dims": 512,
@@ -437,46 +441,45 @@ def measure_e2e(a, w, d, dev, world, runner, barrier):
 
 
 def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e):
-    if True:  # noqa
-        peak, peak_src = measured_peak_gbs()
-        fwd_b, bwd_b = w.algorithmic_bytes()
-        traffic = NCU_DRAM_TRAFFIC.get(w.name, {})
-        line = {
-            "metric": "DFA3D fwd+bwd sampled points/s", "value": value, "unit": "sampled points/s",
-            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 storage, f32 math" if w.value_dtype == "bf16" else "f32",
-            "data": "synthetic",
-            "config": {"workload": w.name, "cameras_per_gpu": w.B, "queries": w.Q, "heads": w.H,
-                       "channels": w.C, "levels": [list(x) for x in w.levels], "points": w.P,
-                       "depth_bins": w.D, "points_per_gpu_step": w.points,
-                       "l2": "inputs per step (%.0f MB) exceed the 126 MB L2; no explicit flush"
-                             % (fwd_b / 1e6)},
-            "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
-            "clocks": clocks,
-            "gpu_launches": runner.launches_per_step * a.steps,
-            "e2e": e2e,
-        }
-        if a.impl == "ours":
-            line["roofline"] = {
-                "kernel": "dfa3d_backward_kernel", "bound": "hbm",
-                "achieved": bwd_b / (bwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                "frac": bwd_b / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic.get("backward"),
-                "algorithmic_bytes": bwd_b, "peak_source": peak_src}
-            line["roofline_forward"] = {
-                "kernel": "dfa3d_forward_kernel", "bound": "hbm",
-                "achieved": fwd_b / (fwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic.get("forward"),
-                "algorithmic_bytes": fwd_b}
-            line["roofline_step"] = {"frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak,
-                                     "algorithmic_bytes": fwd_b + bwd_b}
-            if world == 1 and not a.no_cpu_baseline:
-                line["cpu_baseline"] = cpu_baseline(w, 1)
-        else:
-            line["impl"] = "reference"
-            line["reference_kind"] = ("reference CUDA op (unmodified sources, sm_100a build in "
-                                      "oracle/_ref) through its own autograd Function, same GPU")
-        print(json.dumps(line), flush=True)
+    peak, peak_src = measured_peak_gbs()
+    fwd_b, bwd_b = w.algorithmic_bytes()
+    traffic = NCU_DRAM_TRAFFIC.get(w.name, {})
+    line = {
+        "metric": "DFA3D fwd+bwd sampled points/s", "value": value, "unit": "sampled points/s",
+        "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 storage, f32 math" if w.value_dtype == "bf16" else "f32",
+        "data": "synthetic",
+        "config": {"workload": w.name, "cameras_per_gpu": w.B, "queries": w.Q, "heads": w.H,
+                   "channels": w.C, "levels": [list(x) for x in w.levels], "points": w.P,
+                   "depth_bins": w.D, "points_per_gpu_step": w.points,
+                   "l2": "inputs per step (%.0f MB) exceed the 126 MB L2; no explicit flush"
+                         % (fwd_b / 1e6)},
+        "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
+        "clocks": clocks,
+        "gpu_launches": runner.launches_per_step * a.steps,
+        "e2e": e2e,
+    }
+    if a.impl == "ours":
+        line["roofline"] = {
+            "kernel": "dfa3d_backward_kernel", "bound": "hbm",
+            "achieved": bwd_b / (bwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+            "frac": bwd_b / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic.get("backward"),
+            "algorithmic_bytes": bwd_b, "peak_source": peak_src}
+        line["roofline_forward"] = {
+            "kernel": "dfa3d_forward_kernel", "bound": "hbm",
+            "achieved": fwd_b / (fwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+            "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic.get("forward"),
+            "algorithmic_bytes": fwd_b}
+        line["roofline_step"] = {"frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak,
+                                 "algorithmic_bytes": fwd_b + bwd_b}
+        if world == 1 and not a.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w, 1)
+    else:
+        line["impl"] = "reference"
+        line["reference_kind"] = ("reference CUDA op (unmodified sources, sm_100a build in "
+                                  "oracle/_ref) through its own autograd Function, same GPU")
+    print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
