@@ -11,6 +11,30 @@ import torch
 import torch.distributed as dist
 
 
+def bind_cpu_affinity_to_gpu(index):
+    """Pin the calling process to the CPU cores NVML reports as local to GPU `index` (its NUMA node).
+
+    With one process per GPU this keeps each rank's pinned host buffers and its copy-issuing thread on
+    the socket the GPU hangs off; host<->device streaming of several ranks then does not cross the
+    inter-socket link.  Read-only NVML query plus sched_setaffinity on this process; returns the number
+    of cores bound to, or 0 if NVML or the affinity call is unavailable (nothing is changed then)."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (w >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return 0
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return 0
+
+
 def shard_frames(num_frames, world_size, rank):
     """Contiguous, balanced partition of `num_frames` frames.  Returns range(start, stop); the first
     `num_frames % world_size` ranks get one frame more."""

@@ -318,6 +318,11 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", 0))
     if world != a.gpus:
         log(f"note: --gpus {a.gpus} but WORLD_SIZE={world}; using WORLD_SIZE")
+    if torch.cuda.is_available():
+        from dfa3d_b200 import sharding
+        ncpu = sharding.bind_cpu_affinity_to_gpu(local)     # before any pinned allocation
+        log(f"rank {rank}: bound to {ncpu} CPU cores local to GPU {local}" if ncpu else
+            f"rank {rank}: CPU affinity unchanged")
     if a.workload == "cfg4":
         return run_encoder_stack(a, rank, world, local)
     w = wl.WORKLOADS[a.workload]
@@ -413,7 +418,10 @@ def main():
 
 
 def measure_e2e(a, w, d, dev, world, runner, barrier):
-    host = {k: d[k].pin_memory() for k in ("value", "dist", "loc", "attn", "grad_out")}
+    host = {k: d[k] for k in ("value", "dist", "loc", "attn", "grad_out")}
+    if w.value_dtype == "bf16" and a.impl == "ours":     # bf16 storage starts on the host
+        host["value"], host["dist"] = host["value"].bfloat16(), host["dist"].bfloat16()
+    host = {k: v.pin_memory() for k, v in host.items()}
     pinned_out = {"out": torch.empty(w.B, w.Q, w.H * w.C).pin_memory(),
                   "grad_value": torch.empty_like(d["value"]).pin_memory(),
                   "grad_dist": torch.empty_like(d["dist"]).pin_memory(),
