@@ -51,6 +51,25 @@ def shard_cameras(num_frames, cams_per_frame, world_size, rank):
     return slice(fr.start * cams_per_frame, fr.stop * cams_per_frame)
 
 
+def shard_queries(num_queries, world_size, rank):
+    """Query block of `rank` when ONE batch of frames is split over the ranks (strong scaling): a
+    contiguous, balanced slice of the query dimension.  The value / depth-distribution tensors are
+    then replicated (one broadcast) and the gradients with respect to them are partial sums that
+    need one all-reduce (`allreduce_sum_`)."""
+    r = shard_frames(num_queries, world_size, rank)
+    return slice(r.start, r.stop)
+
+
+def allreduce_sum_(tensors, group=None, async_op=False):
+    """In-place SUM all-reduce of each tensor over the group (the exchange step of the query-block
+    mode: grad_value and grad_dist are partial sums over the ranks' query blocks).  Returns the list of
+    work handles when async_op is set."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return []
+    works = [dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=async_op) for t in tensors]
+    return [w for w in works if w is not None]
+
+
 def max_over_ranks(value, device=None, group=None):
     """Maximum of a per-rank scalar (a device-measured duration) over the process group."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:

@@ -26,6 +26,7 @@ class Workload:
     seed: int = 0
     oob: bool = False                        # ~15 % of points with x or y outside [0,1]
     value_dtype: str = "fp32"                # "fp32" | "bf16" (value and dist storage)
+    local: bool = False                      # locations clustered around per-query reference points
 
     @property
     def L(self):
@@ -67,6 +68,10 @@ WORKLOADS = {
     "cfg2": Workload("cfg2", B=6, levels=_BASE_LEVELS, D=64, Q=10000, P=8, seed=2, oob=True),
     "cfg3": Workload("cfg3", B=6, levels=_BASE_LEVELS, D=64, Q=10000, P=8, seed=3, oob=True,
                      value_dtype="bf16"),
+    # cfg2 with BEVFormer-like locality instead of uniform locations (reported beside the headline):
+    # neighbouring queries look at neighbouring pixels, a query's points stay within a few pixels of
+    # its reference point (spatial_cross_attention.py:513-538 at initialisation)
+    "cfg2local": Workload("cfg2local", B=6, levels=_BASE_LEVELS, D=64, Q=10000, P=8, seed=2, local=True),
     "cfg4op": Workload("cfg4op", B=6, levels=_BASE_LEVELS, D=118, Q=10000, P=8, seed=4, oob=True),
     # small cases for parity tests
     "tiny": Workload("tiny", B=2, levels=((5, 7), (3, 4)), D=5, Q=6, P=3, H=2, C=8, seed=11, oob=True),
@@ -97,6 +102,17 @@ def make_inputs(w: Workload, seed=None, head_repeat=False):
     loc = torch.rand(w.B, w.Q, w.H, w.L, w.P, 3, generator=g)
     if w.oob:
         loc[..., :2] = loc[..., :2] * 1.0846 - 0.0423
+    if w.local:
+        # reference point of query q on a sqrt(Q) x sqrt(Q) grid over the image (row-major, so that
+        # consecutive queries are neighbours), depth from a smooth ramp; offsets of up to ~4 pixels /
+        # ~2 depth bins per (head, level, point), in units of each level's own size
+        side = int(round(w.Q ** 0.5))
+        q = torch.arange(w.Q)
+        ref = torch.stack([((q % side).float() + 0.5) / side, ((q // side).float() + 0.5) / max(1, w.Q // side),
+                           0.15 + 0.7 * (q.float() / w.Q)], -1).clamp(0, 1)          # (Q, 3)
+        size = torch.tensor([[ww, h, w.D] for h, ww in w.levels], dtype=torch.float32)  # (L, 3) = (W, H, D)
+        off = (loc - 0.5) * torch.tensor([8.0, 8.0, 4.0]) / size[None, None, None, :, None, :]
+        loc = ref[None, :, None, None, None, :] + off
     attn = torch.randn(w.B, w.Q, w.H, w.L * w.P, generator=g).softmax(-1).view(w.B, w.Q, w.H, w.L, w.P)
     grad_out = torch.randn(w.B, w.Q, w.H * w.C, generator=g)
     if w.value_dtype == "bf16":

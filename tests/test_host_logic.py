@@ -137,3 +137,37 @@ def test_world_size_2_gloo_sharding_and_gradient_allreduce():
         torch.testing.assert_close(r[3], torch.full((2, 3), 6.0))
         torch.testing.assert_close(r[4], torch.full((2,), 4.0))
         assert r[5] >= 2                                        # tiny buckets -> several collectives
+
+
+def _gloo_query_block_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        qs = sharding.shard_queries(7, world, rank)
+        # a stand-in "gradient": each rank contributes the sum of its query indices
+        g = torch.full((3,), float(sum(range(7)[qs])))
+        works = sharding.allreduce_sum_([g], async_op=True)
+        for w in works:
+            w.wait()
+        q.put((rank, (qs.start, qs.stop), g.clone()))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_world_size_2_gloo_query_block_exchange():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_gloo_query_block_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted((q.get(timeout=120) for _ in range(world)), key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res[0][1] == (0, 4) and res[1][1] == (4, 7)
+    for r in res:                                   # every rank ends with the full sum 0+...+6
+        torch.testing.assert_close(r[2], torch.full((3,), 21.0))
+    assert sharding.allreduce_sum_([torch.ones(1)]) == []      # no process group: nothing to do
