@@ -19,8 +19,6 @@
 
 namespace dfa3d {
 
-enum BwdMode { kFusedBwd = 0, kGivenDepthScoreBwd = 1 };
-
 // Per-lane state of one sampling point that the epilogue needs.
 struct PointState {
   PointGeo g;
@@ -32,7 +30,8 @@ struct PointState {
 
 template <typename DT, int MODE>
 __device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, const ItemCtx &c, int j,
-                                          PointState &s, float (&wgt)[4], int (&off)[4]) {
+                                          const SoftmaxStats &sm, PointState &s, float (&wgt)[4],
+                                          int (&off)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     s.ds[k] = 0.f; s.bw[k] = 0.f; s.lo[k] = 0.f; s.hi[k] = 0.f; wgt[k] = 0.f; off[k] = -1;
@@ -41,15 +40,13 @@ __device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, 
   s.live = false; s.aw = 0.f; s.g.ok2 = false; s.g.ok3 = false;
   if (j >= a.LP) return;
   const int l = j / a.P;
-  const float *lp = c.loc + j * a.loc_stride;
-  const float x = __ldg(lp), y = __ldg(lp + 1);
-  const float z = (MODE == kFusedBwd) ? __ldg(lp + 2) : 0.f;
-  s.aw = __ldg(c.attn + j);
-  s.g = point_geometry(x, y, z, MODE == kFusedBwd, lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N);
+  float x, y, z;
+  read_point<MODE>(a, lv, c, j, l, sm, x, y, z, s.aw);
+  s.g = point_geometry(x, y, z, mode_has_depth(MODE), lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N);
   if (!s.g.ok2) return;
   s.live = true;
   bilinear_weights(s.g, s.bw);
-  if (MODE == kFusedBwd) {
+  if (mode_has_depth(MODE)) {
     const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
                         ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
     const int Dlim = min(s.g.Dd, a.D);
@@ -76,10 +73,12 @@ __device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, 
 }
 
 // Everything that follows from the four dot products t[k] = <value row k, grad_out row>.
+// Returns attention weight x its gradient (the point's term of the softmax-backward dot product;
+// used in caller-fused mode only).
 template <typename DT, int MODE>
-__device__ __forceinline__ void bwd_point_epilogue(const KArgs &a, const ItemCtx &c, int j,
-                                                   const PointState &s, const float (&t)[4]) {
-  if (j >= a.LP) return;
+__device__ __forceinline__ float bwd_point_epilogue(const KArgs &a, const ItemCtx &c, int j,
+                                                    const PointState &s, const float (&t)[4]) {
+  if (j >= a.LP) return 0.f;
   const long long pt = c.pt0 + j;
   float g_attn = 0.f, g_x = 0.f, g_y = 0.f, g_z = 0.f;
   float gds[4] = {0.f, 0.f, 0.f, 0.f};
@@ -96,7 +95,7 @@ __device__ __forceinline__ void bwd_point_epilogue(const KArgs &a, const ItemCtx
     const float e0 = s.ds[0] * tt[0], e1 = s.ds[1] * tt[1], e2 = s.ds[2] * tt[2], e3 = s.ds[3] * tt[3];
     g_x = (float)s.g.W * s.aw * (hh * (e1 - e0) + s.g.lh * (e2 - e3));
     g_y = (float)s.g.Hh * s.aw * (hw * (e3 - e0) + s.g.lw * (e2 - e1));
-    if (MODE == kFusedBwd && s.g.ok3) {
+    if (mode_has_depth(MODE) && s.g.ok3) {
       float *gd_bh = a.grad_dist + ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
       const float hd = 1.f - s.g.ld;
       const int Dlim = min(s.g.Dd, a.D);
@@ -113,13 +112,38 @@ __device__ __forceinline__ void bwd_point_epilogue(const KArgs &a, const ItemCtx
       g_z = (float)s.g.Dd * acc;
     }
   }
+  if (MODE == kCallerFused) {
+    // d loc / d offset = 1 / (W, H, D); the logit gradient needs the whole item's dot product and is
+    // finished by finish_logit_grads(): park the attention gradient in its slot for now
+    a.grad_logits[pt] = g_attn;
+    float *gu = a.grad_off_uv + pt * 2;
+    gu[0] = s.live ? __fdiv_rn(g_x, (float)s.g.W) : 0.f;
+    gu[1] = s.live ? __fdiv_rn(g_y, (float)s.g.Hh) : 0.f;
+    a.grad_off_d[pt] = __fdiv_rn(g_z, (float)a.D);
+    return s.aw * g_attn;
+  }
   a.grad_attn[pt] = g_attn;
   float *gl = a.grad_loc + pt * a.loc_stride;
   gl[0] = g_x;
   gl[1] = g_y;
-  if (MODE == kFusedBwd) gl[2] = g_z;
+  if (MODE == kFused) gl[2] = g_z;
   if (a.grad_ds_out)
     reinterpret_cast<float4 *>(a.grad_ds_out)[pt] = make_float4(gds[0], gds[1], gds[2], gds[3]);
+  return 0.f;
+}
+
+// Softmax backward of the item's logits: grad_logit_j = a_j * (g_j - sum_k a_k g_k).  `partial` is the
+// lane's share of the sum; the g_j were parked in grad_logits by the epilogue (each lane re-reads only
+// what it wrote itself).
+__device__ __forceinline__ void finish_logit_grads(const KArgs &a, const ItemCtx &c, int lane,
+                                                   const SoftmaxStats &sm, float partial) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, s);
+  for (int j = lane; j < a.LP; j += 32) {
+    const long long pt = c.pt0 + j;
+    const float aw = __fdiv_rn(expf(__ldg(a.logits + pt) - sm.mx), sm.sum);
+    a.grad_logits[pt] = aw * (a.grad_logits[pt] - partial);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -162,11 +186,15 @@ dfa3d_backward_kernel(const KArgs a) {
     }
   }
 
+  SoftmaxStats sm{0.f, 1.f};
+  if (MODE == kCallerFused) sm = item_softmax_stats(a, c, lane);
+  float dot = 0.f;
+
   for (int chunk = 0; chunk < a.LP; chunk += 32) {
     PointState st;
     float wgt[4];
     int off[4];
-    bwd_point<DT, MODE>(a, lv, c, chunk + lane, st, wgt, off);
+    bwd_point<DT, MODE>(a, lv, c, chunk + lane, sm, st, wgt, off);
     store_rows(rows[warp], lane, off, wgt);
     __syncwarp();
     auto step = [&](int r0, int nrows) {
@@ -210,9 +238,10 @@ dfa3d_backward_kernel(const KArgs a) {
     __syncwarp();
     const float4 tq = reinterpret_cast<const float4 *>(dots[warp])[lane];
     const float t[4] = {tq.x, tq.y, tq.z, tq.w};
-    bwd_point_epilogue<DT, MODE>(a, c, chunk + lane, st, t);
+    dot += bwd_point_epilogue<DT, MODE>(a, c, chunk + lane, st, t);
     __syncwarp();
   }
+  if (MODE == kCallerFused) finish_logit_grads(a, c, lane, sm, dot);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -235,11 +264,14 @@ dfa3d_backward_generic_kernel(const KArgs a) {
   const float *gop = a.grad_out + c.item * C;
   RowEntry *my = rows[warp];
   float *myd = dots[warp];
+  SoftmaxStats sm{0.f, 1.f};
+  if (MODE == kCallerFused) sm = item_softmax_stats(a, c, lane);
+  float dot = 0.f;
   for (int chunk = 0; chunk < a.LP; chunk += 32) {
     PointState st;
     float wgt[4];
     int off[4];
-    bwd_point<DT, MODE>(a, lv, c, chunk + lane, st, wgt, off);
+    bwd_point<DT, MODE>(a, lv, c, chunk + lane, sm, st, wgt, off);
     store_rows(my, lane, off, wgt);
     __syncwarp();
     const int nrows = min(32, a.LP - chunk) * 4;
@@ -260,9 +292,10 @@ dfa3d_backward_generic_kernel(const KArgs a) {
     __syncwarp();
     const float4 tq = reinterpret_cast<const float4 *>(myd)[lane];
     const float t[4] = {tq.x, tq.y, tq.z, tq.w};
-    bwd_point_epilogue<DT, MODE>(a, c, chunk + lane, st, t);
+    dot += bwd_point_epilogue<DT, MODE>(a, c, chunk + lane, st, t);
     __syncwarp();
   }
+  if (MODE == kCallerFused) finish_logit_grads(a, c, lane, sm, dot);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -341,18 +374,23 @@ static cudaError_t launch_backward_vd(const KArgs &a0, cudaStream_t s) {
   return cudaSuccess;
 }
 
-cudaError_t launch_backward(const KArgs &a, bool value_bf16, bool dist_bf16, bool given_ds,
-                            cudaStream_t s) {
-  if (a.items == 0) return cudaSuccess;
-  if (given_ds) {
-    return value_bf16 ? launch_backward_vd<__nv_bfloat16, float, kGivenDepthScoreBwd>(a, s)
-                      : launch_backward_vd<float, float, kGivenDepthScoreBwd>(a, s);
-  }
+template <int MODE>
+static cudaError_t launch_backward_m(const KArgs &a, bool value_bf16, bool dist_bf16, cudaStream_t s) {
   if (value_bf16)
-    return dist_bf16 ? launch_backward_vd<__nv_bfloat16, __nv_bfloat16, kFusedBwd>(a, s)
-                     : launch_backward_vd<__nv_bfloat16, float, kFusedBwd>(a, s);
-  return dist_bf16 ? launch_backward_vd<float, __nv_bfloat16, kFusedBwd>(a, s)
-                   : launch_backward_vd<float, float, kFusedBwd>(a, s);
+    return dist_bf16 ? launch_backward_vd<__nv_bfloat16, __nv_bfloat16, MODE>(a, s)
+                     : launch_backward_vd<__nv_bfloat16, float, MODE>(a, s);
+  return dist_bf16 ? launch_backward_vd<float, __nv_bfloat16, MODE>(a, s)
+                   : launch_backward_vd<float, float, MODE>(a, s);
+}
+
+cudaError_t launch_backward(const KArgs &a, bool value_bf16, bool dist_bf16, int mode, cudaStream_t s) {
+  if (a.items == 0) return cudaSuccess;
+  if (mode == kGivenDepthScore) {
+    return value_bf16 ? launch_backward_vd<__nv_bfloat16, float, kGivenDepthScore>(a, s)
+                      : launch_backward_vd<float, float, kGivenDepthScore>(a, s);
+  }
+  if (mode == kCallerFused) return launch_backward_m<kCallerFused>(a, value_bf16, dist_bf16, s);
+  return launch_backward_m<kFused>(a, value_bf16, dist_bf16, s);
 }
 
 cudaError_t launch_depth_score_backward(const KArgs &a, bool dist_bf16, cudaStream_t s) {

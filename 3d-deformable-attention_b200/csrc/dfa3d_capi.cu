@@ -136,8 +136,8 @@ int dfa3d_wms_attn_forward(const dfa3d_problem *p, const void *value, const int6
   dfa3d::KArgs a = base_args(p, 2, 2);
   a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn;
   a.ds_in = depth_score; a.out = out;
-  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16, false, true,
-                                      (cudaStream_t)stream),
+  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16, false,
+                                      dfa3d::kGivenDepthScore, (cudaStream_t)stream),
                 "dfa3d_wms_attn_forward launch");
 }
 
@@ -157,8 +157,8 @@ int dfa3d_wms_attn_backward(const dfa3d_problem *p, const void *value, const int
   a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn;
   a.ds_in = depth_score; a.grad_out = grad_out; a.grad_value = grad_value; a.grad_loc = grad_loc2;
   a.grad_attn = grad_attn; a.grad_ds_out = grad_depth_score;
-  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16, false, true,
-                                       (cudaStream_t)stream),
+  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16, false,
+                                       dfa3d::kGivenDepthScore, (cudaStream_t)stream),
                 "dfa3d_wms_attn_backward launch");
 }
 
@@ -174,7 +174,8 @@ int dfa3d_fused_forward(const dfa3d_problem *p, const void *value, const void *d
   a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
   a.attn = attn; a.out = out; a.ds_out = depth_score_out;
   return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16,
-                                      p->dist_dtype == DFA3D_DTYPE_BF16, false, (cudaStream_t)stream),
+                                      p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kFused,
+                                      (cudaStream_t)stream),
                 "dfa3d_fused_forward launch");
 }
 
@@ -193,8 +194,58 @@ int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *
   a.attn = attn; a.grad_out = grad_out; a.grad_value = grad_value; a.grad_dist = grad_dist;
   a.grad_loc = grad_loc3; a.grad_attn = grad_attn;
   return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16,
-                                       p->dist_dtype == DFA3D_DTYPE_BF16, false, (cudaStream_t)stream),
+                                       p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kFused,
+                                       (cudaStream_t)stream),
                 "dfa3d_fused_backward launch");
+}
+
+int dfa3d_attn3d_forward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
+                         const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                         const float *ref_points, const float *offsets_uv, const float *offsets_depth,
+                         const float *logits, float *out, void *stream) {
+  if (int rc = check_problem(p, true, true)) return rc;
+  if (num_anchors <= 0 || p->P % num_anchors != 0)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "num_anchors=%d must be positive and divide P=%d",
+                num_anchors, p->P);
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start);
+  REQUIRE_PTR(ref_points); REQUIRE_PTR(offsets_uv); REQUIRE_PTR(offsets_depth); REQUIRE_PTR(logits);
+  REQUIRE_PTR(out);
+  REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(out);
+  dfa3d::KArgs a = base_args(p, 3, 3);
+  a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.ref = ref_points;
+  a.off_uv = offsets_uv; a.off_d = offsets_depth; a.logits = logits; a.Z = num_anchors; a.out = out;
+  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16,
+                                      p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kCallerFused,
+                                      (cudaStream_t)stream),
+                "dfa3d_attn3d_forward launch");
+}
+
+int dfa3d_attn3d_backward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
+                          const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                          const float *ref_points, const float *offsets_uv,
+                          const float *offsets_depth, const float *logits, const float *grad_out,
+                          float *grad_value, float *grad_dist, float *grad_offsets_uv,
+                          float *grad_offsets_depth, float *grad_logits, void *stream) {
+  if (int rc = check_problem(p, true, true)) return rc;
+  if (num_anchors <= 0 || p->P % num_anchors != 0)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "num_anchors=%d must be positive and divide P=%d",
+                num_anchors, p->P);
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start);
+  REQUIRE_PTR(ref_points); REQUIRE_PTR(offsets_uv); REQUIRE_PTR(offsets_depth); REQUIRE_PTR(logits);
+  REQUIRE_PTR(grad_out); REQUIRE_PTR(grad_value); REQUIRE_PTR(grad_dist); REQUIRE_PTR(grad_offsets_uv);
+  REQUIRE_PTR(grad_offsets_depth); REQUIRE_PTR(grad_logits);
+  REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(grad_out); REQUIRE_ALIGNED(grad_value);
+  dfa3d::KArgs a = base_args(p, 3, 3);
+  a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.ref = ref_points;
+  a.off_uv = offsets_uv; a.off_d = offsets_depth; a.logits = logits; a.Z = num_anchors;
+  a.grad_out = grad_out; a.grad_value = grad_value; a.grad_dist = grad_dist;
+  a.grad_off_uv = grad_offsets_uv; a.grad_off_d = grad_offsets_depth; a.grad_logits = grad_logits;
+  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16,
+                                       p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kCallerFused,
+                                       (cudaStream_t)stream),
+                "dfa3d_attn3d_backward launch");
 }
 
 }  // extern "C"

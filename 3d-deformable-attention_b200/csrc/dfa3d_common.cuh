@@ -20,6 +20,15 @@
 namespace dfa3d {
 
 constexpr int kMaxLevels = 32;
+
+// What the kernels are given per sampling point.
+//   kFused            location (x,y,z) + attention weight; depth scores computed from dist
+//   kGivenDepthScore  location (x,y) + attention weight + the four depth scores (two-stage API)
+//   kCallerFused      reference point + raw offsets + raw attention logits: the caller's location
+//                     assembly and softmax (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/
+//                     spatial_cross_attention.py:498-538) happen in the prologue; depth scores from dist
+enum Mode { kFused = 0, kGivenDepthScore = 1, kCallerFused = 2 };
+__host__ __device__ constexpr bool mode_has_depth(int m) { return m != kGivenDepthScore; }
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
 
@@ -33,6 +42,15 @@ struct KArgs {
   const float *attn;       // (B,Q,H,L,P)
   const float *ds_in;      // (B,Q,H,L,P,4) given depth score (two-stage attention)
   const float *grad_out;   // (B,Q,H*C)
+  // caller-fused mode: locations and attention weights are formed inside the kernel
+  const float *ref;        // (B,Q,Z,3) reference points
+  const float *off_uv;     // (B,Q,H,L,P,2) raw x/y offsets in pixels
+  const float *off_d;      // (B,Q,H,L,P) raw depth offsets in bins
+  const float *logits;     // (B,Q,H,L*P) raw attention logits
+  float *grad_off_uv;      // (B,Q,H,L,P,2), overwritten
+  float *grad_off_d;       // (B,Q,H,L,P), overwritten
+  float *grad_logits;      // (B,Q,H,L*P), overwritten
+  int Z;                   // reference points (pillar anchors) per query
   const float *grad_ds_in; // (B,Q,H,L,P,4) incoming depth-score gradient (two-stage depth backward)
   float *out;              // (B,Q,H*C)
   float *ds_out;           // (B,Q,H,L,P,4) or null
@@ -71,6 +89,7 @@ __device__ __forceinline__ void stage_levels(LevelTable &t, const KArgs &a) {
 // the per-point and per-row arithmetic stays 32-bit.
 struct ItemCtx {
   int b, h;
+  long long bq;             // b*Q + q
   long long item;           // (b*Q + q)*H + h
   const float *loc;         // first location of the item
   const float *attn;        // first attention weight of the item
@@ -83,12 +102,58 @@ __device__ __forceinline__ bool item_context(const KArgs &a, int warp, ItemCtx &
   const unsigned idx = blockIdx.x * kWarpsPerCta + warp;
   if (idx >= (unsigned)a.items_per_cam) return false;
   c.b = (int)blockIdx.y + a.b0;
-  c.h = (int)(idx % (unsigned)a.H);
+  const unsigned q = idx / (unsigned)a.H;
+  c.h = (int)(idx - q * (unsigned)a.H);
+  c.bq = (long long)c.b * a.Q + q;
   c.item = (long long)c.b * a.items_per_cam + idx;
   c.pt0 = c.item * a.LP;
-  c.loc = a.loc + c.pt0 * a.loc_stride;
+  c.loc = a.loc + c.pt0 * a.loc_stride;      // (not dereferenced in caller-fused mode)
   c.attn = a.attn + c.pt0;
   return true;
+}
+
+// Softmax of an item's L*P attention logits (caller-fused mode): maximum and sum of exp(l - max),
+// formed with warp shuffles; lane j later turns its own logit into exp(l_j - max) / sum.
+struct SoftmaxStats {
+  float mx, sum;
+};
+
+__device__ __forceinline__ SoftmaxStats item_softmax_stats(const KArgs &a, const ItemCtx &c, int lane) {
+  const float *lg = a.logits + c.pt0;
+  float mx = -INFINITY;
+  for (int j = lane; j < a.LP; j += 32) mx = fmaxf(mx, __ldg(lg + j));
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+  float sum = 0.f;
+  for (int j = lane; j < a.LP; j += 32) sum += expf(__ldg(lg + j) - mx);
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+  return SoftmaxStats{mx, sum};
+}
+
+// Location and attention weight of point j of the item, from whatever the mode provides.
+// Caller-fused: loc = reference point of the point's anchor + offset / (W, H, D), the division and the
+// addition rounded separately as the tensor expressions of the caller are
+// (spatial_cross_attention.py:527-533); anchor of point p of a level = p % Z (:530-531).
+template <int MODE>
+__device__ __forceinline__ void read_point(const KArgs &a, const LevelTable &lv, const ItemCtx &c, int j,
+                                           int l, const SoftmaxStats &sm, float &x, float &y, float &z,
+                                           float &aw) {
+  if (MODE == kCallerFused) {
+    const int zi = (j - l * a.P) % a.Z;
+    const float *r = a.ref + (c.bq * a.Z + zi) * 3;
+    const float *o = a.off_uv + (c.pt0 + j) * 2;
+    x = __fadd_rn(__ldg(r), __fdiv_rn(__ldg(o), (float)lv.w[l]));
+    y = __fadd_rn(__ldg(r + 1), __fdiv_rn(__ldg(o + 1), (float)lv.h[l]));
+    z = __fadd_rn(__ldg(r + 2), __fdiv_rn(__ldg(a.off_d + c.pt0 + j), (float)a.D));
+    aw = __fdiv_rn(expf(__ldg(a.logits + c.pt0 + j) - sm.mx), sm.sum);
+  } else {
+    const float *lp = c.loc + j * a.loc_stride;
+    x = __ldg(lp);
+    y = __ldg(lp + 1);
+    z = (MODE == kFused) ? __ldg(lp + 2) : 0.f;
+    aw = __ldg(c.attn + j);
+  }
 }
 
 // Geometry of one sampling point.

@@ -22,27 +22,25 @@
 
 namespace dfa3d {
 
-enum FwdMode { kFused = 0, kGivenDepthScore = 1 };
-
 // ------------------------------------------------------------------------------------------------
 // prologue: per-lane point -> 4 row entries (+ depth scores)
 // ------------------------------------------------------------------------------------------------
 template <typename DT, int MODE>
 __device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, const ItemCtx &c, int j,
-                                          float (&ds)[4], float (&wgt)[4], int (&off)[4]) {
+                                          const SoftmaxStats &sm, float (&ds)[4], float (&wgt)[4],
+                                          int (&off)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) { ds[k] = 0.f; wgt[k] = 0.f; off[k] = -1; }
   if (j >= a.LP) return;
   const int l = j / a.P;
-  const float *lp = c.loc + j * a.loc_stride;
-  const float x = __ldg(lp), y = __ldg(lp + 1);
-  const float z = (MODE == kFused) ? __ldg(lp + 2) : 0.f;
-  const float aw = __ldg(c.attn + j);
-  const PointGeo g = point_geometry(x, y, z, MODE == kFused, lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N);
+  float x, y, z, aw;
+  read_point<MODE>(a, lv, c, j, l, sm, x, y, z, aw);
+  const PointGeo g = point_geometry(x, y, z, mode_has_depth(MODE), lv.h[l], lv.w[l], lv.d[l], lv.start[l],
+                                    a.N);
   if (!g.ok2) return;
   float bw[4];
   bilinear_weights(g, bw);
-  if (MODE == kFused) {
+  if (mode_has_depth(MODE)) {
     const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
                         ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
     float lo[4], hi[4];
@@ -99,11 +97,13 @@ dfa3d_forward_kernel(const KArgs a) {
   float acc[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) acc[i] = 0.f;
+  SoftmaxStats sm{0.f, 1.f};
+  if (MODE == kCallerFused) sm = item_softmax_stats(a, c, lane);
 
   for (int chunk = 0; chunk < a.LP; chunk += 32) {
     float ds[4], wgt[4];
     int off[4];
-    fwd_point<DT, MODE>(a, lv, c, chunk + lane, ds, wgt, off);
+    fwd_point<DT, MODE>(a, lv, c, chunk + lane, sm, ds, wgt, off);
     store_rows(rows[warp], lane, off, wgt);
     if (WRITE_DS && chunk + lane < a.LP)
       reinterpret_cast<float4 *>(a.ds_out)[c.pt0 + chunk + lane] = make_float4(ds[0], ds[1], ds[2], ds[3]);
@@ -168,13 +168,15 @@ dfa3d_forward_generic_kernel(const KArgs a) {
   const int C = a.C;
   const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)c.b * a.N * a.H + c.h) * C;
   RowEntry *my = rows[warp];
+  SoftmaxStats sm{0.f, 1.f};
+  if (MODE == kCallerFused) sm = item_softmax_stats(a, c, lane);
   for (int c0 = 0; c0 < C; c0 += 32) {          // C <= 1024: at most 32 passes
     const int ch = c0 + lane;
     float acc = 0.f;
     for (int chunk = 0; chunk < a.LP; chunk += 32) {
       float ds[4], wgt[4];
       int off[4];
-      fwd_point<DT, MODE>(a, lv, c, chunk + lane, ds, wgt, off);
+      fwd_point<DT, MODE>(a, lv, c, chunk + lane, sm, ds, wgt, off);
       store_rows(my, lane, off, wgt);
       if (WRITE_DS && c0 == 0 && chunk + lane < a.LP)
         reinterpret_cast<float4 *>(a.ds_out)[c.pt0 + chunk + lane] =
@@ -265,18 +267,23 @@ static cudaError_t launch_forward_vd(const KArgs &a0, cudaStream_t s) {
   return cudaSuccess;
 }
 
-cudaError_t launch_forward(const KArgs &a, bool value_bf16, bool dist_bf16, bool given_ds,
-                           cudaStream_t s) {
+template <int MODE>
+static cudaError_t launch_forward_m(const KArgs &a, bool value_bf16, bool dist_bf16, cudaStream_t s) {
+  if (value_bf16)
+    return dist_bf16 ? launch_forward_vd<__nv_bfloat16, __nv_bfloat16, MODE>(a, s)
+                     : launch_forward_vd<__nv_bfloat16, float, MODE>(a, s);
+  return dist_bf16 ? launch_forward_vd<float, __nv_bfloat16, MODE>(a, s)
+                   : launch_forward_vd<float, float, MODE>(a, s);
+}
+
+cudaError_t launch_forward(const KArgs &a, bool value_bf16, bool dist_bf16, int mode, cudaStream_t s) {
   if (a.items == 0) return cudaSuccess;
-  if (given_ds) {   // dist is not read: its type parameter is irrelevant
+  if (mode == kGivenDepthScore) {   // dist is not read: its type parameter is irrelevant
     return value_bf16 ? launch_forward_vd<__nv_bfloat16, float, kGivenDepthScore>(a, s)
                       : launch_forward_vd<float, float, kGivenDepthScore>(a, s);
   }
-  if (value_bf16)
-    return dist_bf16 ? launch_forward_vd<__nv_bfloat16, __nv_bfloat16, kFused>(a, s)
-                     : launch_forward_vd<__nv_bfloat16, float, kFused>(a, s);
-  return dist_bf16 ? launch_forward_vd<float, __nv_bfloat16, kFused>(a, s)
-                   : launch_forward_vd<float, float, kFused>(a, s);
+  if (mode == kCallerFused) return launch_forward_m<kCallerFused>(a, value_bf16, dist_bf16, s);
+  return launch_forward_m<kFused>(a, value_bf16, dist_bf16, s);
 }
 
 cudaError_t launch_depth_score_forward(const KArgs &a, bool dist_bf16, cudaStream_t s) {

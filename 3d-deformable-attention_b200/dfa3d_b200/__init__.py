@@ -8,6 +8,8 @@ operators raise.
 from . import _lib, ext  # noqa: F401
 from .host import HostPipeline  # noqa: F401
 from .functions import (  # noqa: F401
+    DeformableAttn3DFromOffsetsFunction,
+    DeformableAttn3DFromOffsetsFunction_fp32,
     MultiScale3DDeformableAttnFunction,
     MultiScale3DDeformableAttnFunction_fp32,
     MultiScaleDepthScoreSampleFunction,
@@ -22,4 +24,5 @@ __all__ = [
     "MultiScale3DDeformableAttnFunction",
     "MultiScaleDepthScoreSampleFunction_fp32", "WeightedMultiScaleDeformableAttnFunction_fp32",
     "MultiScale3DDeformableAttnFunction_fp32",
+    "DeformableAttn3DFromOffsetsFunction", "DeformableAttn3DFromOffsetsFunction_fp32",
 ]

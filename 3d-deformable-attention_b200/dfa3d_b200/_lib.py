@@ -37,6 +37,11 @@ ENTRY_POINTS = {
     "dfa3d_fused_forward": 9,
     "dfa3d_fused_backward": 12,
 }
+# entry points that take `int32_t num_anchors` right after the descriptor
+ENTRY_POINTS_WITH_ANCHORS = {
+    "dfa3d_attn3d_forward": 10,
+    "dfa3d_attn3d_backward": 15,
+}
 
 _lib = None
 
@@ -59,6 +64,10 @@ def load():
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [_P] + [_V] * nptr
+    for name, nptr in ENTRY_POINTS_WITH_ANCHORS.items():
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [_P, ctypes.c_int32] + [_V] * nptr
     got = lib.dfa3d_abi_version()
     if got != ABI_VERSION:
         raise ImportError(f"libdfa3d_b200.so has ABI version {got}, this package expects {ABI_VERSION}")

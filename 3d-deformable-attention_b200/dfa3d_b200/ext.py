@@ -250,3 +250,79 @@ def dfa3d_fused_backward(value, value_dpt_dist, value_spatial_shapes, value_leve
                   _ptr(sampling_locations), _ptr(attention_weights), _ptr(grad_output),
                   _ptr(grad_value), _ptr(grad_value_dpt_dist), _ptr(grad_sampling_loc),
                   _ptr(grad_attn_weight), _stream(value))
+
+
+# ------------------------------------------------------------------------------------------------
+# caller-fused entry points: the location assembly and the softmax of the attention module happen
+# inside the kernels (BEVFormer_DFA3D/.../spatial_cross_attention.py:503-538)
+# ------------------------------------------------------------------------------------------------
+def _attn3d_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits):
+    _chk(value, "value", _VAL); _chk(dist, "value_dpt_dist", _VAL)
+    _chk(shapes3, "spatial_shapes", _I64); _chk(lsi, "level_start_index", _I64)
+    for t, n in ((ref, "reference_points"), (off_uv, "sampling_offsets_uv"),
+                 (off_d, "sampling_offsets_depth"), (logits, "attention_logits")):
+        _chk(t, n, _F32)
+    _same_device(value, dist, shapes3, lsi, ref, off_uv, off_d, logits)
+    B, N, H, C = value.shape
+    if off_uv.dim() != 6 or off_uv.shape[-1] != 2:
+        raise RuntimeError(f"sampling_offsets_uv must be (B,Q,H,L,P,2), got {tuple(off_uv.shape)}")
+    Bq, Q, Hq, L, P, _ = off_uv.shape
+    Bd, Nd, D, hs = _dist_problem(dist, H)
+    if ref.dim() != 4 or ref.shape[-1] != 3 or tuple(ref.shape[:2]) != (B, Q):
+        raise RuntimeError(f"reference_points must be (B,Q,Z,3), got {tuple(ref.shape)}")
+    Z = ref.shape[2]
+    if Z <= 0 or P % Z != 0:
+        raise RuntimeError(f"the number of anchors ({Z}) must divide the points per level ({P})")
+    if (Bq, Hq) != (B, H) or (Bd, Nd) != (B, N) or tuple(shapes3.shape) != (L, 3) \
+            or off_d.numel() != B * Q * H * L * P or logits.numel() != B * Q * H * L * P:
+        raise RuntimeError("inconsistent shapes between value, value_dpt_dist, spatial_shapes (L,3), "
+                           "offsets and logits")
+    return _lib.Problem(B, N, H, C, D, L, Q, P, _dt(value), _dt(dist), hs), Z, (B, Q, H, C)
+
+
+def dfa3d_attn3d_forward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                         reference_points, sampling_offsets_uv, sampling_offsets_depth,
+                         attention_logits, out=None):
+    """value (B,N,H,C); value_dpt_dist (B,N,D)|(B,N,H,D); reference_points (B,Q,Z,3);
+    sampling_offsets_uv (B,Q,H,L,P,2) in pixels; sampling_offsets_depth (B,Q,H,L,P) in bins;
+    attention_logits (B,Q,H,L*P) before the softmax.  Returns output (B,Q,H*C)."""
+    pr, Z, (B, Q, H, C) = _attn3d_problem(value, value_dpt_dist, value_spatial_shapes,
+                                          value_level_start_index, reference_points,
+                                          sampling_offsets_uv, sampling_offsets_depth, attention_logits)
+    if out is None:
+        out = torch.empty((B, Q, H * C), dtype=torch.float32, device=value.device)
+    else:
+        _chk(out, "out", _F32)
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_attn3d_forward", pr, Z, _ptr(value), _ptr(value_dpt_dist),
+                  _ptr(value_spatial_shapes), _ptr(value_level_start_index), _ptr(reference_points),
+                  _ptr(sampling_offsets_uv), _ptr(sampling_offsets_depth), _ptr(attention_logits),
+                  _ptr(out), _stream(value))
+    return out
+
+
+def dfa3d_attn3d_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                          reference_points, sampling_offsets_uv, sampling_offsets_depth,
+                          attention_logits, grad_output, grad_value, grad_value_dpt_dist,
+                          grad_offsets_uv, grad_offsets_depth, grad_logits):
+    """Accumulates into grad_value / grad_value_dpt_dist (float32, caller-zeroed); overwrites the
+    gradients of the offsets and of the logits."""
+    pr, Z, (B, Q, H, C) = _attn3d_problem(value, value_dpt_dist, value_spatial_shapes,
+                                          value_level_start_index, reference_points,
+                                          sampling_offsets_uv, sampling_offsets_depth, attention_logits)
+    for t, n in ((grad_output, "grad_output"), (grad_value, "grad_value"),
+                 (grad_value_dpt_dist, "grad_value_dpt_dist"), (grad_offsets_uv, "grad_offsets_uv"),
+                 (grad_offsets_depth, "grad_offsets_depth"), (grad_logits, "grad_logits")):
+        _chk(t, n, _F32)
+    if grad_output.numel() != B * Q * H * C or grad_value.shape != value.shape \
+            or grad_value_dpt_dist.shape != value_dpt_dist.shape \
+            or grad_offsets_uv.shape != sampling_offsets_uv.shape \
+            or grad_offsets_depth.numel() != sampling_offsets_depth.numel() \
+            or grad_logits.numel() != attention_logits.numel():
+        raise RuntimeError("inconsistent shapes in dfa3d_attn3d_backward")
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_attn3d_backward", pr, Z, _ptr(value), _ptr(value_dpt_dist),
+                  _ptr(value_spatial_shapes), _ptr(value_level_start_index), _ptr(reference_points),
+                  _ptr(sampling_offsets_uv), _ptr(sampling_offsets_depth), _ptr(attention_logits),
+                  _ptr(grad_output), _ptr(grad_value), _ptr(grad_value_dpt_dist), _ptr(grad_offsets_uv),
+                  _ptr(grad_offsets_depth), _ptr(grad_logits), _stream(value))

@@ -112,6 +112,41 @@ class MultiScale3DDeformableAttnFunction(Function):
         return grad_value, grad_dist, None, None, grad_sampling_loc, grad_attn_weight, None, None
 
 
+class DeformableAttn3DFromOffsetsFunction(Function):
+    """The one-stage operator fed with what the attention module's Linear layers produce: reference
+    points, raw sampling offsets (pixels / depth bins) and raw attention logits.  The division by the
+    level sizes, the addition of the reference points and the softmax over levels x points
+    (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/spatial_cross_attention.py:503-538) run
+    in the kernels' prologue, so neither the (B,Q,H,L,P,3) location tensor nor the attention weights
+    nor their gradients are ever materialised.  No counterpart in the reference: it calls its Function
+    with the assembled tensors.  The reference points receive no gradient."""
+
+    @staticmethod
+    def forward(ctx, value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                reference_points, sampling_offsets_uv, sampling_offsets_depth, attention_logits):
+        output = ext_module.dfa3d_attn3d_forward(
+            value, value_dpt_dist, value_spatial_shapes, value_level_start_index, reference_points,
+            sampling_offsets_uv, sampling_offsets_depth, attention_logits)
+        ctx.save_for_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                              reference_points, sampling_offsets_uv, sampling_offsets_depth,
+                              attention_logits)
+        return output
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        value, dist, shapes, lsi, ref, off_uv, off_d, logits = ctx.saved_tensors
+        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_dist = torch.zeros(dist.shape, dtype=torch.float32, device=dist.device)
+        grad_uv = torch.empty_like(off_uv)
+        grad_d = torch.empty_like(off_d)
+        grad_logits = torch.empty_like(logits)
+        ext_module.dfa3d_attn3d_backward(value, dist, shapes, lsi, ref, off_uv, off_d, logits,
+                                         grad_output.contiguous(), grad_value, grad_dist, grad_uv, grad_d,
+                                         grad_logits)
+        return grad_value, grad_dist, None, None, None, grad_uv, grad_d, grad_logits
+
+
 def _fp32_variant(cls, name):
     """Same Function with inputs cast to float32 when autocast is active."""
     fwd = torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float32)(cls.forward)
@@ -125,3 +160,5 @@ WeightedMultiScaleDeformableAttnFunction_fp32 = _fp32_variant(
     WeightedMultiScaleDeformableAttnFunction, "WeightedMultiScaleDeformableAttnFunction_fp32")
 MultiScale3DDeformableAttnFunction_fp32 = _fp32_variant(
     MultiScale3DDeformableAttnFunction, "MultiScale3DDeformableAttnFunction_fp32")
+DeformableAttn3DFromOffsetsFunction_fp32 = _fp32_variant(
+    DeformableAttn3DFromOffsetsFunction, "DeformableAttn3DFromOffsetsFunction_fp32")

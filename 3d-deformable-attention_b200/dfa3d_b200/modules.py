@@ -17,7 +17,7 @@ import math
 import torch
 import torch.nn as nn
 
-from .functions import MultiScale3DDeformableAttnFunction_fp32
+from .functions import DeformableAttn3DFromOffsetsFunction_fp32, MultiScale3DDeformableAttnFunction_fp32
 
 
 def assemble_sampling_locations(reference_points, offsets_uv, offsets_depth, spatial_shapes, depth_bins):
@@ -44,8 +44,11 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
     """3-D deformable attention over multi-level camera features and their depth distributions."""
 
     def __init__(self, embed_dims=256, num_heads=8, num_levels=4, num_points=8, im2col_step=64,
-                 batch_first=True, compute_weight_update=True):
+                 batch_first=True, compute_weight_update=True, fuse_input_ops=True):
         super().__init__()
+        # fuse_input_ops: let the kernels form the sampling locations and the softmax from the Linear
+        # outputs (used whenever weight_update is not needed; numerically the same operations)
+        self.fuse_input_ops = fuse_input_ops
         # weight_update (:579) needs the (B,Q,H,L,P,4) depth_score tensor written out; callers that do
         # not use it (SpatialCrossAttention_DFA3D with use_empty=False) can switch it off
         self.compute_weight_update = compute_weight_update
@@ -97,14 +100,20 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
         if key_padding_mask is not None:
             value = value.masked_fill(key_padding_mask[..., None], 0.0)
         value = value.view(bs, N, H, -1)
-        off_uv = self.sampling_offsets(query).view(bs, Q, H, L, P, 2)
-        off_d = self.sampling_offsets_depth(query).view(bs, Q, H, L, P, 1)
-        attn = self.attention_weights(query).view(bs, Q, H, L * P).softmax(-1).view(bs, Q, H, L, P)
         if reference_points.shape[-1] != 3:
             raise ValueError("Last dim of reference_points must be 3 (x, y, depth), but got "
                              f"{reference_points.shape[-1]} instead.")
-        loc = assemble_sampling_locations(reference_points, off_uv, off_d, spatial_shapes, D)
         shapes3 = torch.cat([spatial_shapes, torch.full_like(spatial_shapes[:, :1], D)], -1).contiguous()
+        off_uv = self.sampling_offsets(query).view(bs, Q, H, L, P, 2)
+        off_d = self.sampling_offsets_depth(query).view(bs, Q, H, L, P, 1)
+        logits = self.attention_weights(query).view(bs, Q, H, L * P)
+        if self.fuse_input_ops and not self.compute_weight_update:
+            output = DeformableAttn3DFromOffsetsFunction_fp32.apply(
+                value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
+                reference_points.contiguous(), off_uv, off_d, logits)
+            return (output if self.batch_first else output.permute(1, 0, 2)), None
+        attn = logits.softmax(-1).view(bs, Q, H, L, P)
+        loc = assemble_sampling_locations(reference_points, off_uv, off_d, spatial_shapes, D)
         if self.compute_weight_update:
             output, depth_score = MultiScale3DDeformableAttnFunction_fp32.apply(
                 value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,

@@ -115,6 +115,29 @@ int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *
                          const float *attn, const float *grad_out, float *grad_value,
                          float *grad_dist, float *grad_loc3, float *grad_attn, void *stream);
 
+/* The attention module's tensor code folded into the operator.  Replaces, around the one-stage
+ * Function, the location assembly and the softmax of MSDeformableAttention3D_DFA3D.forward
+ * (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/spatial_cross_attention.py:503-538):
+ *   loc[b,q,h,l,p] = ref_points[b,q,p % num_anchors] + (offsets_uv / (w_l, h_l), offsets_depth / D)
+ *   attn[b,q,h,:]  = softmax over the L*P logits
+ * ref_points (B,Q,num_anchors,3), offsets_uv (B,Q,H,L,P,2), offsets_depth (B,Q,H,L,P),
+ * logits (B,Q,H,L*P), all fp32; num_anchors must divide P.  Writes every element of out. */
+int dfa3d_attn3d_forward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
+                         const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                         const float *ref_points, const float *offsets_uv, const float *offsets_depth,
+                         const float *logits, float *out, void *stream);
+
+/* Backward of dfa3d_attn3d_forward, i.e. of the Function's backward (:306-352) chained with the
+ * autograd of the division, the addition and the softmax.  grad_value and grad_dist are ACCUMULATED
+ * into (caller zeroes them); grad_offsets_uv, grad_offsets_depth and grad_logits are overwritten.
+ * The reference points get no gradient (in BEVFormer they come from fixed geometry). */
+int dfa3d_attn3d_backward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
+                          const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                          const float *ref_points, const float *offsets_uv,
+                          const float *offsets_depth, const float *logits, const float *grad_out,
+                          float *grad_value, float *grad_dist, float *grad_offsets_uv,
+                          float *grad_offsets_depth, float *grad_logits, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -151,3 +151,48 @@ def dfa3d_backward(value, dist, shapes3, lsi, loc3, attn, grad_out, depth_score=
     grad_dist, grad_loc3 = ms_depth_score_sample_backward(dist, shapes3, lsi, loc3, grad_ds)
     grad_loc3[..., :2] += grad_loc2
     return grad_value, grad_dist, grad_loc3, grad_attn
+
+
+# ----------------------------------------------------------------------------------------------
+# the attention module's tensor code around the operator
+# (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/spatial_cross_attention.py:503-538)
+# ----------------------------------------------------------------------------------------------
+def _assemble(ref, off_uv, off_d, shapes3, dtype):
+    """:513-538 -> (loc (B,Q,H,L,P,3), normalizer (L,3) = (w, h, D))."""
+    shapes3 = _i64(shapes3)
+    B, Q, H, L, P, _ = off_uv.shape
+    Z = ref.shape[2]
+    norm = np.stack([shapes3[:, 1], shapes3[:, 0], shapes3[:, 2]], -1).astype(dtype)
+    off = np.concatenate([off_uv, off_d.reshape(B, Q, H, L, P, 1)], -1) / norm[None, None, None, :, None, :]
+    loc = ref[:, :, None, None, None, :, :] + off.reshape(B, Q, H, L, P // Z, Z, 3)
+    return np.ascontiguousarray(loc.reshape(B, Q, H, L, P, 3), dtype=dtype), norm
+
+
+def _softmax(logits):
+    """:503-511, over the flattened levels x points."""
+    e = np.exp(logits - logits.max(-1, keepdims=True))
+    return e / e.sum(-1, keepdims=True)
+
+
+def attn3d_forward(value, dist, shapes3, lsi, ref, off_uv, off_d, logits):
+    """Reference points (B,Q,Z,3) + raw offsets (B,Q,H,L,P,2|1) + raw logits (B,Q,H,L*P) -> output."""
+    dt = np.asarray(value).dtype
+    B, Q, H, L, P, _ = off_uv.shape
+    loc, _ = _assemble(np.asarray(ref, dt), np.asarray(off_uv, dt), np.asarray(off_d, dt), shapes3, dt)
+    attn = _softmax(np.asarray(logits, dt).reshape(B, Q, H, L * P)).reshape(B, Q, H, L, P).astype(dt)
+    out, _ = dfa3d_forward(value, dist, shapes3, lsi, loc, attn)
+    return out
+
+
+def attn3d_backward(value, dist, shapes3, lsi, ref, off_uv, off_d, logits, grad_out):
+    """Chain rule of the division, the addition and the softmax around dfa3d_backward.
+    Returns (grad_value, grad_dist, grad_off_uv, grad_off_d, grad_logits)."""
+    dt = np.asarray(value).dtype
+    B, Q, H, L, P, _ = off_uv.shape
+    loc, norm = _assemble(np.asarray(ref, dt), np.asarray(off_uv, dt), np.asarray(off_d, dt), shapes3, dt)
+    attn = _softmax(np.asarray(logits, dt).reshape(B, Q, H, L * P)).astype(dt)
+    gv, gd, gl, ga = dfa3d_backward(value, dist, shapes3, lsi, loc, attn.reshape(B, Q, H, L, P), grad_out)
+    g_off = gl / norm[None, None, None, :, None, :]
+    ga = ga.reshape(B, Q, H, L * P)
+    g_logits = attn * (ga - (attn * ga).sum(-1, keepdims=True))
+    return gv, gd, g_off[..., :2].copy(), g_off[..., 2].copy(), g_logits

@@ -20,6 +20,7 @@ def test_header_declares_the_expected_entry_points():
     names = declared_symbols()
     for n in ("dfa3d_depth_score_forward", "dfa3d_depth_score_backward", "dfa3d_wms_attn_forward",
               "dfa3d_wms_attn_backward", "dfa3d_fused_forward", "dfa3d_fused_backward",
+              "dfa3d_attn3d_forward", "dfa3d_attn3d_backward",
               "dfa3d_last_error", "dfa3d_abi_version"):
         assert n in names
 
@@ -33,7 +34,8 @@ def test_library_exports_every_declared_symbol(lib_built):
 def test_binding_table_matches_header(lib_built):
     from dfa3d_b200 import _lib
     declared = set(declared_symbols()) - {"dfa3d_last_error", "dfa3d_abi_version"}
-    assert declared <= set(_lib.ENTRY_POINTS) , declared - set(_lib.ENTRY_POINTS)
+    bound = set(_lib.ENTRY_POINTS) | set(_lib.ENTRY_POINTS_WITH_ANCHORS)
+    assert declared <= bound, declared - bound
     assert _lib.load().dfa3d_abi_version() == _lib.ABI_VERSION
 
 
@@ -69,6 +71,11 @@ def test_validation_returns_codes_not_crashes(lib_built):
     empty = _lib.Problem(0, 4, 1, 4, 2, 1, 0, 1, 0, 0, 2)
     for name, n in _lib.ENTRY_POINTS.items():
         assert getattr(lib, name)(ctypes.byref(empty), *([None] * n)) == 0, name
+    for name, n in _lib.ENTRY_POINTS_WITH_ANCHORS.items():
+        assert getattr(lib, name)(ctypes.byref(empty), 1, *([None] * n)) == 0, name
+    # the anchors must divide the points per level
+    assert lib.dfa3d_attn3d_forward(ctypes.byref(ok), 3, *([None] * 10)) == -1
+    assert b"num_anchors" in lib.dfa3d_last_error()
     with pytest.raises(RuntimeError, match="invalid argument"):
         _lib.call("dfa3d_fused_forward", ok, *([None] * 9))
 

@@ -58,6 +58,8 @@ def test_spatial_cross_attention_matches_grid_sample_form(lib_built, monkeypatch
     g1 = {n: p.grad.clone() for n, p in sca.named_parameters()}
     gq1 = q1.grad.clone()
     sca.zero_grad()
+    # reference path: the module's own tensor expressions + the independent grid_sample formulation
+    attn.fuse_input_ops = False
     monkeypatch.setattr(modules, "MultiScale3DDeformableAttnFunction_fp32", _GridSampleOp)
     q2 = d["query"].clone().requires_grad_(True)
     out2 = sca(q2, None, d["value"], d["value_dpt_dist"], d["reference_points_cam"], d["bev_mask"],
@@ -67,6 +69,38 @@ def test_spatial_cross_attention_matches_grid_sample_form(lib_built, monkeypatch
     torch.testing.assert_close(gq1, q2.grad, rtol=1e-3, atol=1e-5)
     for n, p in sca.named_parameters():
         torch.testing.assert_close(g1[n], p.grad, rtol=1e-3, atol=1e-4, msg=lambda m, n=n: f"{n}: {m}")
+
+
+def test_module_paths_agree(lib_built):
+    """The three ways the attention module can call the operator give the same output and gradients:
+    offsets/logits fused into the kernels, assembled tensors without depth_score, and the reference's
+    way (assembled tensors, depth_score materialised for weight_update)."""
+    torch.manual_seed(2)
+    d = _inputs(7, cams=2)
+    res = []
+    for fuse, wu in ((True, False), (False, False), (False, True)):
+        torch.manual_seed(2)
+        attn = modules.MSDeformableAttention3D_DFA3D(embed_dims=32, num_heads=2, num_levels=2,
+                                                     num_points=8, fuse_input_ops=fuse,
+                                                     compute_weight_update=wu).to(DEV)
+        with torch.no_grad():
+            for p in (attn.sampling_offsets.weight, attn.sampling_offsets_depth.weight,
+                      attn.attention_weights.weight):
+                p.normal_(0, 0.05)
+        q = d["query"][:, :20].clone().requires_grad_(True)
+        value = d["value"][0].permute(1, 0, 2).contiguous()          # (bs, N, E)
+        dist = d["value_dpt_dist"][0].permute(1, 0, 2).contiguous()
+        ref = d["reference_points_cam"][0][:, :20].contiguous()     # (bs, Q, Z, 3)
+        out, wupd = attn(q, value, dist, ref, d["spatial_shapes"], d["level_start_index"])
+        assert (wupd is not None) == wu
+        out.pow(2).sum().backward()
+        res.append((out.detach(), q.grad.clone(), {n: p.grad.clone() for n, p in attn.named_parameters()}))
+    for other in res[1:]:
+        torch.testing.assert_close(res[0][0], other[0], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(res[0][1], other[1], rtol=1e-4, atol=1e-6)
+        for n in res[0][2]:
+            torch.testing.assert_close(res[0][2][n], other[2][n], rtol=1e-4, atol=1e-5,
+                                       msg=lambda m, n=n: f"{n}: {m}")
 
 
 def test_encoder_stack_trains_one_step(lib_built):

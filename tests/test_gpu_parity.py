@@ -312,3 +312,84 @@ def test_host_pipeline_matches_device_path(M):
         assert_close("grad_dist", host_out["grad_dist"], gd, **BWD)
     with pytest.raises(RuntimeError, match="pinned"):
         pipe.run({k: v.clone() for k, v in d.items()}, host_out)
+
+
+def test_mixed_storage_types_match_oracle(M):
+    """fp32 value with bf16 dist and the reverse: each tensor's storage type is independent."""
+    from dfa3d_b200 import ext
+    w = wl.WORKLOADS["odd"].with_(value_dtype="bf16", seed=21, C=32)
+    d = wl.make_inputs(w, head_repeat=True)
+    ref = oracle_all(d, np.float32)
+    t = {k: v.to(DEV) for k, v in d.items()}
+    for vb, db in ((False, True), (True, False)):
+        value = t["value"].bfloat16() if vb else t["value"]
+        dist = t["dist"].bfloat16() if db else t["dist"]
+        out, ds = ext.dfa3d_fused_forward(value, dist, t["shapes"], t["lsi"], t["loc"], t["attn"], 64)
+        gv = torch.zeros_like(t["value"]); gd = torch.zeros_like(t["dist"])
+        gl = torch.empty_like(t["loc"]); ga = torch.empty_like(t["attn"])
+        ext.dfa3d_fused_backward(value, dist, t["shapes"], t["lsi"], t["loc"], t["attn"], t["grad_out"], gv,
+                                 gd, gl, ga, 64)
+        check_against(dict(out=out, ds=ds, grad_value=gv, grad_dist=gd, grad_loc=gl, grad_attn=ga), ref,
+                      False)
+
+
+def test_more_cameras_than_one_launch_covers(M):
+    """The camera index is the grid's y dimension (limit 65535): larger batches take several launches."""
+    from dfa3d_b200 import ext
+    B = 65535 + 3
+    w = wl.WORKLOADS["tiny"].with_(B=B, levels=((2, 2),), Q=1, H=1, C=8, P=2, D=2, seed=5)
+    d = wl.make_inputs(w, head_repeat=True)
+    t = {k: v.to(DEV) for k, v in d.items()}
+    out, _ = ext.dfa3d_fused_forward(t["value"], t["dist"], t["shapes"], t["lsi"], t["loc"], t["attn"], B)
+    gv = torch.zeros_like(t["value"]); gd = torch.zeros_like(t["dist"])
+    gl = torch.empty_like(t["loc"]); ga = torch.empty_like(t["attn"])
+    ext.dfa3d_fused_backward(t["value"], t["dist"], t["shapes"], t["lsi"], t["loc"], t["attn"],
+                             t["grad_out"], gv, gd, gl, ga, B)
+    # the last cameras (second launch) against the oracle on just those cameras
+    tail = {k: (v[-5:].contiguous() if k not in ("shapes", "lsi") else v) for k, v in d.items()}
+    ref = oracle_all(tail, np.float32)
+    assert_close("out", out[-5:], ref["out"], **FWD)
+    assert_close("grad_value", gv[-5:], ref["grad_value"], **BWD)
+    assert_close("grad_loc", gl[-5:], ref["grad_loc"], **BWD)
+    assert_close("grad_dist", gd[-5:], ref["grad_dist"], **BWD)
+
+
+ATTN3D_CASES = {
+    "LP8_Z2": dict(levels=((5, 7), (3, 4)), P=4, Z=2),
+    "LP32_Z4": dict(levels=((6, 5), (4, 4), (3, 3), (2, 3)), P=8, Z=4),
+    "LP45_Z3_two_chunks": dict(levels=((6, 5), (4, 4), (3, 3), (2, 3), (1, 1)), P=9, Z=3),
+    "C12_generic_Z1": dict(levels=((5, 7), (3, 4)), P=3, Z=1, C=12),
+}
+
+
+@pytest.mark.parametrize("case", sorted(ATTN3D_CASES))
+@pytest.mark.parametrize("shared_dist", [False, True], ids=["dist_per_head", "dist_shared"])
+def test_offsets_and_logits_entry_points_match_oracle(M, case, shared_dist):
+    """Caller-fused path: reference points + raw offsets + raw logits in, softmax and location assembly
+    inside the kernels; against the oracle's composition of the same tensor expressions."""
+    import dfa3d_oracle as O
+    kw = dict(ATTN3D_CASES[case]); Z = kw.pop("Z")
+    w = wl.WORKLOADS["tiny"].with_(name=case, seed=40 + Z, Q=11, **kw)
+    d = wl.make_inputs(w, head_repeat=True)
+    g = torch.Generator().manual_seed(w.seed)
+    ref_pts = torch.rand(w.B, w.Q, Z, 3, generator=g) * 1.2 - 0.1
+    off_uv = torch.randn(w.B, w.Q, w.H, w.L, w.P, 2, generator=g) * 1.5
+    off_d = torch.randn(w.B, w.Q, w.H, w.L, w.P, generator=g)
+    logits = torch.randn(w.B, w.Q, w.H, w.L * w.P, generator=g)
+    n = {k: v.numpy() for k, v in d.items()}
+    o_out = O.attn3d_forward(n["value"], n["dist"], n["shapes"], n["lsi"], ref_pts.numpy(), off_uv.numpy(),
+                             off_d.numpy(), logits.numpy())
+    o_g = O.attn3d_backward(n["value"], n["dist"], n["shapes"], n["lsi"], ref_pts.numpy(), off_uv.numpy(),
+                            off_d.numpy(), logits.numpy(), n["grad_out"])
+    dist = d["dist"][:, :, 0].contiguous() if shared_dist else d["dist"]
+    leaves = [t.to(DEV).requires_grad_(True) for t in (d["value"], dist, off_uv, off_d, logits)]
+    out = M.DeformableAttn3DFromOffsetsFunction.apply(
+        leaves[0], leaves[1], d["shapes"].to(DEV), d["lsi"].to(DEV), ref_pts.to(DEV), leaves[2], leaves[3],
+        leaves[4])
+    out.backward(d["grad_out"].to(DEV))
+    assert_close("out", out, o_out, **FWD)
+    assert_close("grad_value", leaves[0].grad, o_g[0], **BWD)
+    assert_close("grad_dist", leaves[1].grad, o_g[1].sum(2) if shared_dist else o_g[1], **BWD)
+    assert_close("grad_offsets_uv", leaves[2].grad, o_g[2], **BWD)
+    assert_close("grad_offsets_depth", leaves[3].grad, o_g[3], **BWD)
+    assert_close("grad_logits", leaves[4].grad, o_g[4], **BWD)

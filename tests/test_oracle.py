@@ -160,3 +160,35 @@ def test_empty_and_ragged_shapes():
     loc = np.zeros((1, 0, 2, 1, 5, 3)); attn = np.zeros((1, 0, 2, 1, 5))
     out, ds = O.dfa3d_forward(value, dist, shapes, lsi, loc, attn)
     assert out.shape == (1, 0, 8) and ds.shape == (1, 0, 2, 1, 5, 4)
+
+
+def test_attn3d_composition_matches_torch_autograd_fp64():
+    """Oracle of the caller-fused entry points (offsets + logits in) against PyTorch autograd through
+    the module's own tensor expressions and the independent grid_sample formulation."""
+    import grid_sample_form as G
+    from dfa3d_b200 import modules
+    g = torch.Generator().manual_seed(3)
+    B, Q, H, C, D, Z, P = 2, 5, 2, 4, 6, 2, 4
+    levels = ((5, 7), (3, 4))
+    L = len(levels); N = sum(h * w for h, w in levels)
+    shapes3 = torch.tensor([[h, w, D] for h, w in levels]); lsi = torch.tensor([0, 35])
+    value = torch.randn(B, N, H, C, generator=g, dtype=torch.float64)
+    dist = torch.randn(B, N, H, D, generator=g, dtype=torch.float64).softmax(-1)
+    ref = torch.rand(B, Q, Z, 3, generator=g, dtype=torch.float64)
+    off_uv = torch.randn(B, Q, H, L, P, 2, generator=g, dtype=torch.float64, requires_grad=True)
+    off_d = torch.randn(B, Q, H, L, P, 1, generator=g, dtype=torch.float64, requires_grad=True)
+    logits = torch.randn(B, Q, H, L * P, generator=g, dtype=torch.float64, requires_grad=True)
+    go = torch.randn(B, Q, H * C, generator=g, dtype=torch.float64)
+    loc = modules.assemble_sampling_locations(ref, off_uv, off_d, shapes3[:, :2], D)
+    attn = logits.softmax(-1).view(B, Q, H, L, P)
+    out = G.dfa3d_grid_sample(value, dist, shapes3.tolist(), lsi.tolist(), loc, attn)
+    out.backward(go)
+    n = lambda t: t.detach().numpy()
+    o_out = O.attn3d_forward(n(value), n(dist), n(shapes3), n(lsi), n(ref), n(off_uv), n(off_d)[..., 0],
+                             n(logits))
+    gv, gd, guv, gdd, glg = O.attn3d_backward(n(value), n(dist), n(shapes3), n(lsi), n(ref), n(off_uv),
+                                              n(off_d)[..., 0], n(logits), n(go))
+    assert_close("out", o_out, n(out), rtol=1e-11, atol=1e-13)
+    assert_close("grad_off_uv", guv, n(off_uv.grad), rtol=1e-10, atol=1e-12)
+    assert_close("grad_off_d", gdd, n(off_d.grad)[..., 0], rtol=1e-10, atol=1e-12)
+    assert_close("grad_logits", glg, n(logits.grad), rtol=1e-10, atol=1e-12)
