@@ -579,6 +579,10 @@ def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e)
         line["impl"] = "reference"
         line["reference_kind"] = ("reference CUDA op (unmodified sources, sm_100a build in "
                                   "oracle/_ref) through its own autograd Function, same GPU")
+        if world == 1 and not a.no_cpu_baseline:
+            # the reference has no CPU implementation of this path; the CPU figure beside it is the
+            # C + OpenMP port of its kernels
+            line["cpu_baseline"] = cpu_baseline(w, 1)
     print(json.dumps(line), flush=True)
 
 
