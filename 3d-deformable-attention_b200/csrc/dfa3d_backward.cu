@@ -5,7 +5,7 @@
 //   prologue -- the lane recomputes its point's geometry and per-corner depth scores from `dist`
 //               (fused mode; the (B,Q,H,L,P,4) depth_score tensor is never read back) and publishes
 //               {row offset, a * bilinear * depth score} per corner in shared memory;
-//   rows     -- a group of G lanes reads one value row (16-byte loads), takes its dot product with
+//   rows     -- a group of G lanes reads one value row (4 channels per lane), takes its dot product with
 //               the item's grad_out row (xor-shuffles inside the group) and adds
 //               weight * grad_out to grad_value with one 16-byte vector reduction per lane
 //               (red.global.add.v4.f32) instead of one scalar atomic per channel;
@@ -147,16 +147,16 @@ __device__ __forceinline__ void finish_logit_grads(const KArgs &a, const ItemCtx
 }
 
 // ------------------------------------------------------------------------------------------------
-// fused / given-depth-score backward, C a power of two with 16-byte row fragments
+// fused / given-depth-score backward, C/4 a power of two
 // ------------------------------------------------------------------------------------------------
 // fp32 value: 4 CTAs (32 warps) per SM is the measured optimum (64 registers, a few bytes of spill);
 // bf16 value carries twice the channels per lane and would spill heavily under that cap.
-template <typename VT> constexpr int backward_min_ctas() { return sizeof(VT) == 4 ? 4 : 1; }
+template <typename VT> constexpr int backward_min_ctas() { return 4; }
 
 template <typename VT, typename DT, int C, int MODE, bool FULL>
 __global__ void __launch_bounds__(kThreads, backward_min_ctas<VT>())
 dfa3d_backward_kernel(const KArgs a) {
-  constexpr int V = RowVec<VT>::kElems;
+  constexpr int V = RowVec4<VT>::kElems;
   constexpr int G = C / V;
   constexpr int R = 32 / G;
   constexpr int U = 4;
@@ -208,7 +208,7 @@ dfa3d_backward_kernel(const KArgs a) {
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         if (e[u].off >= 0) {
-          RowVec<VT>::load(vbase + e[u].off, v[u]);
+          RowVec4<VT>::load(vbase + e[u].off, v[u]);
         } else {
 #pragma unroll
           for (int i = 0; i < V; ++i) v[u][i] = 0.f;
@@ -348,7 +348,7 @@ dfa3d_depth_score_backward_kernel(const KArgs a) {
 // ------------------------------------------------------------------------------------------------
 template <typename VT, typename DT, int MODE, bool FULL>
 static void launch_backward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
-  constexpr int V = RowVec<VT>::kElems;
+  constexpr int V = RowVec4<VT>::kElems;
   switch ((a.C % V == 0) ? a.C / V : 0) {
     case 2:  dfa3d_backward_kernel<VT, DT, 2 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 4:  dfa3d_backward_kernel<VT, DT, 4 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;

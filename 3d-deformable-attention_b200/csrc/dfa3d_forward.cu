@@ -7,7 +7,8 @@
 //                that give the four per-corner depth scores; it leaves one {row offset, weight} pair
 //                per corner in the warp's slice of shared memory;
 //   gather    -- the warp walks the (point, corner) rows; a group of G lanes reads one value row with
-//                16-byte loads, so one warp-wide request fetches 32/G rows, and every lane
+//                16-byte loads (4 fp32 or 8 bf16 channels per lane), so one warp-wide request fetches
+//                32/G rows, and every lane
 //                accumulates weight * row fragment;
 //   epilogue  -- the 32/G partial sums are folded with xor-shuffles and G lanes store the output row.
 // This replaces the reference's pair of kernels (one thread per (b,q,h) for the depth scores,
@@ -70,14 +71,14 @@ __device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, 
 }
 
 // ------------------------------------------------------------------------------------------------
-// fused / given-depth-score forward, C/V a power of two (V = elements per 16-byte fragment)
+// fused / given-depth-score / caller-fused forward; C/V a power of two, V = channels per 16 bytes
 // ------------------------------------------------------------------------------------------------
 // 5 CTAs (40 warps) per SM: measured best; at 6+ the register cap starts to cost more than the
 // extra warps hide.
 template <typename VT, typename DT, int C, int MODE, bool WRITE_DS, bool FULL>
 __global__ void __launch_bounds__(kThreads, 5)
 dfa3d_forward_kernel(const KArgs a) {
-  constexpr int V = RowVec<VT>::kElems;   // elements per 16-byte fragment
+  constexpr int V = RowVec<VT>::kElems;   // channels per lane
   constexpr int G = C / V;                // lanes per row
   constexpr int R = 32 / G;               // rows per warp-wide request
   constexpr int U = 4;                    // requests in flight per lane
@@ -108,7 +109,7 @@ dfa3d_forward_kernel(const KArgs a) {
     if (WRITE_DS && chunk + lane < a.LP)
       reinterpret_cast<float4 *>(a.ds_out)[c.pt0 + chunk + lane] = make_float4(ds[0], ds[1], ds[2], ds[3]);
     __syncwarp();
-    // R*U rows per step: U independent 16-byte loads in flight per lane, then U fused multiply-adds.
+    // R*U rows per step: U independent row-fragment loads in flight per lane, then U fused multiply-adds.
     auto step = [&](int r0, int nrows) {
       RowEntry e[U];
       float v[U][V];

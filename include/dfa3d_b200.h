@@ -46,7 +46,8 @@ typedef struct dfa3d_problem {
   int32_t B;  /* batch * cameras */
   int32_t N;  /* pixels over all levels */
   int32_t H;  /* heads */
-  int32_t C;  /* channels per head (multiple of 4 for fp32 value, of 8 for bf16) */
+  int32_t C;  /* channels per head (any value up to DFA3D_MAX_CHANNELS; C/4 in {2,4,8,16} takes the
+                 vectorised kernels) */
   int32_t D;  /* depth bins = channel count of dist */
   int32_t L;  /* levels */
   int32_t Q;  /* queries */
