@@ -222,19 +222,39 @@ __device__ __forceinline__ void store_rows(RowEntry *table, int lane, const int 
   dst[1] = make_uint4((uint32_t)off[2], __float_as_uint(wgt[2]), (uint32_t)off[3], __float_as_uint(wgt[3]));
 }
 
+// Two adjacent depth bins p[0], p[1] that are both in range: one naturally aligned 8-byte (fp32) or
+// 4-byte (bf16) load when the pair happens to be aligned, two scalar loads otherwise (the second then
+// hits the sector the first brought into L1).  Measured 3-5 % on the kernels against always-scalar;
+// wider windows with element extraction were measured slower.
+__device__ __forceinline__ void load_pair(const float *p, float &lo, float &hi) {
+  if ((reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+    const float2 t = __ldg(reinterpret_cast<const float2 *>(p));
+    lo = t.x; hi = t.y;
+  } else {
+    lo = __ldg(p); hi = __ldg(p + 1);
+  }
+}
+__device__ __forceinline__ void load_pair(const __nv_bfloat16 *p, float &lo, float &hi) {
+  if ((reinterpret_cast<uintptr_t>(p) & 3) == 0) {
+    const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(p));
+    lo = __uint_as_float(t << 16); hi = __uint_as_float(t & 0xffff0000u);
+  } else {
+    lo = load_scalar(p); hi = load_scalar(p + 1);
+  }
+}
+
 // The two depth bins z0, z0+1 of one corner pixel (0 where a bin is outside [0, Dlim-1] or the corner
-// is unusable).  Dlim = min(depth size of the level, channel count of dist).  Two scalar loads: the
-// second one hits the sector the first one brought into L1.  (One aligned 16-byte window load per
-// pair was measured slower: the forward is issue-bound and the element extraction costs more
-// instructions than the second load.)
+// is unusable).  Dlim = min(depth size of the level, channel count of dist).
 template <typename DT>
 __device__ __forceinline__ void load_depth_pair(const DT *dist_bh, int pix_stride, int pix, int z0,
                                                 int Dlim, bool ok3, float &lo, float &hi) {
   lo = 0.f; hi = 0.f;
   if (ok3 && pix >= 0) {
     const DT *p = dist_bh + ((long long)pix * pix_stride + z0);
-    if (z0 >= 0 && z0 < Dlim) lo = load_scalar(p);
-    if (z0 + 1 < Dlim) hi = load_scalar(p + 1);
+    const bool vlo = z0 >= 0 && z0 < Dlim, vhi = z0 + 1 < Dlim;
+    if (vlo && vhi) load_pair(p, lo, hi);
+    else if (vlo) lo = load_scalar(p);
+    else if (vhi) hi = load_scalar(p + 1);
   }
 }
 

@@ -94,3 +94,19 @@ def test_shim_rejects_cpu_tensors_like_the_reference(lib_built):
         ext.wms_deform_attn_forward(d["value"], d["shapes"][:, :2].contiguous(), d["lsi"],
                                     d["loc"][..., :2].contiguous(), d["attn"],
                                     torch.zeros(*d["attn"].shape, 4), 64)
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    """No fallback path: without the shared library the package raises, it does not compute."""
+    import subprocess
+    import sys
+    pkg = os.path.join(ROOT, "3d-deformable-attention_b200")
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "import torch, dfa3d_b200\n"
+        "from dfa3d_b200 import _lib\n"
+        "try:\n    _lib.load()\nexcept ImportError as e:\n    assert 'no fallback' in str(e); print('raised')\n"
+        % pkg)
+    env = dict(os.environ, DFA3D_B200_LIB=str(tmp_path / "absent.so"))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env)
+    assert r.returncode == 0 and "raised" in r.stdout, r.stderr

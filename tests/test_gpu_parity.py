@@ -393,3 +393,22 @@ def test_offsets_and_logits_entry_points_match_oracle(M, case, shared_dist):
     assert_close("grad_offsets_uv", leaves[2].grad, o_g[2], **BWD)
     assert_close("grad_offsets_depth", leaves[3].grad, o_g[3], **BWD)
     assert_close("grad_logits", leaves[4].grad, o_g[4], **BWD)
+
+
+def test_fp32_variant_casts_under_autocast(M):
+    """The `_fp32` Functions run in float32 inside an autocast region, like the reference's
+    custom_fwd(cast_inputs=torch.float32) variants."""
+    d = {k: v.to(DEV) for k, v in wl.make_inputs(wl.WORKLOADS["tiny"]).items()}
+    ref, _ = M.MultiScale3DDeformableAttnFunction.apply(d["value"], d["dist"], d["shapes"], d["lsi"],
+                                                        d["loc"], d["attn"], 64)
+    v = d["value"].clone().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.float16):
+        out, ds = M.MultiScale3DDeformableAttnFunction_fp32.apply(
+            v.half(), d["dist"].half(), d["shapes"], d["lsi"], d["loc"], d["attn"], 64)
+        assert out.dtype == torch.float32 and ds.dtype == torch.float32
+    out.sum().backward()
+    assert v.grad is not None and torch.isfinite(v.grad).all()
+    # inputs went through fp16 once: same result as feeding the fp16-rounded values in fp32
+    ref16, _ = M.MultiScale3DDeformableAttnFunction.apply(d["value"].half().float(), d["dist"].half().float(),
+                                                          d["shapes"], d["lsi"], d["loc"], d["attn"], 64)
+    assert torch.equal(out, ref16) and not torch.equal(ref, ref16)
