@@ -189,10 +189,11 @@ __device__ __forceinline__ PointGeo point_geometry(float x, float y, float z, bo
   const bool xl = x0 >= 0, xh = x1 <= W - 1, yl = y0 >= 0, yh = y1 <= Hh - 1;
   const int base = start + y0 * W + x0;
   const int p0 = base, p1 = base + 1, p2 = base + W + 1, p3 = base + W;
-  g.pix[0] = (g.ok2 && yl && xl && p0 < N) ? p0 : -1;
-  g.pix[1] = (g.ok2 && yl && xh && p1 < N) ? p1 : -1;
-  g.pix[2] = (g.ok2 && yh && xh && p2 < N) ? p2 : -1;
-  g.pix[3] = (g.ok2 && yh && xl && p3 < N) ? p3 : -1;
+  const unsigned n = (unsigned)N;      // unsigned compare: also rejects indices that wrapped negative
+  g.pix[0] = (g.ok2 && yl && xl && (unsigned)p0 < n) ? p0 : -1;
+  g.pix[1] = (g.ok2 && yl && xh && (unsigned)p1 < n) ? p1 : -1;
+  g.pix[2] = (g.ok2 && yh && xh && (unsigned)p2 < n) ? p2 : -1;
+  g.pix[3] = (g.ok2 && yh && xl && (unsigned)p3 < n) ? p3 : -1;
   return g;
 }
 
