@@ -57,7 +57,8 @@ __device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, 
 #pragma unroll
     for (int k = 0; k < 4; ++k) s.ds[k] = s.g.ok3 ? s.lo[k] * hd + s.hi[k] * s.g.ld : 0.f;
   } else {
-    const float4 t = __ldg(reinterpret_cast<const float4 *>(a.ds_in) + (c.pt0 + j));
+    const float4 t = a.ds_in ? __ldg(reinterpret_cast<const float4 *>(a.ds_in) + (c.pt0 + j))
+                             : make_float4(1.f, 1.f, 1.f, 1.f);
     s.ds[0] = s.g.pix[0] >= 0 ? t.x : 0.f;
     s.ds[1] = s.g.pix[1] >= 0 ? t.y : 0.f;
     s.ds[2] = s.g.pix[2] >= 0 ? t.z : 0.f;

@@ -199,6 +199,39 @@ int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *
                 "dfa3d_fused_backward launch");
 }
 
+int dfa3d_msda_forward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
+                       const int64_t *level_start, const float *loc2, const float *attn, float *out,
+                       void *stream) {
+  if (int rc = check_problem(p, true, false)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(shapes2); REQUIRE_PTR(level_start); REQUIRE_PTR(loc2);
+  REQUIRE_PTR(attn); REQUIRE_PTR(out);
+  REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(out);
+  dfa3d::KArgs a = base_args(p, 2, 2);
+  a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn; a.out = out;
+  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16, false,
+                                      dfa3d::kGivenDepthScore, (cudaStream_t)stream),
+                "dfa3d_msda_forward launch");
+}
+
+int dfa3d_msda_backward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
+                        const int64_t *level_start, const float *loc2, const float *attn,
+                        const float *grad_out, float *grad_value, float *grad_loc2, float *grad_attn,
+                        void *stream) {
+  if (int rc = check_problem(p, true, false)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(shapes2); REQUIRE_PTR(level_start); REQUIRE_PTR(loc2);
+  REQUIRE_PTR(attn); REQUIRE_PTR(grad_out); REQUIRE_PTR(grad_value); REQUIRE_PTR(grad_loc2);
+  REQUIRE_PTR(grad_attn);
+  REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(grad_out); REQUIRE_ALIGNED(grad_value);
+  dfa3d::KArgs a = base_args(p, 2, 2);
+  a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn;
+  a.grad_out = grad_out; a.grad_value = grad_value; a.grad_loc = grad_loc2; a.grad_attn = grad_attn;
+  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16, false,
+                                       dfa3d::kGivenDepthScore, (cudaStream_t)stream),
+                "dfa3d_msda_backward launch");
+}
+
 int dfa3d_attn3d_forward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
                          const void *dist, const int64_t *shapes3, const int64_t *level_start,
                          const float *ref_points, const float *offsets_uv, const float *offsets_depth,

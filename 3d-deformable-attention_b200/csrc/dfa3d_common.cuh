@@ -23,7 +23,8 @@ constexpr int kMaxLevels = 32;
 
 // What the kernels are given per sampling point.
 //   kFused            location (x,y,z) + attention weight; depth scores computed from dist
-//   kGivenDepthScore  location (x,y) + attention weight + the four depth scores (two-stage API)
+//   kGivenDepthScore  location (x,y) + attention weight + the four depth scores (two-stage API);
+//                     without a depth-score tensor the scores are 1: plain 2-D deformable attention
 //   kCallerFused      reference point + raw offsets + raw attention logits: the caller's location
 //                     assembly and softmax (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/
 //                     spatial_cross_attention.py:498-538) happen in the prologue; depth scores from dist

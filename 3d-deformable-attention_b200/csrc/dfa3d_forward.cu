@@ -53,7 +53,9 @@ __device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, 
 #pragma unroll
     for (int k = 0; k < 4; ++k) ds[k] = g.ok3 ? lo[k] * hd + hi[k] * g.ld : 0.f;
   } else {
-    const float4 t = __ldg(reinterpret_cast<const float4 *>(a.ds_in) + (c.pt0 + j));
+    // no depth-score tensor = plain 2-D multi-scale deformable attention: every in-image corner counts 1
+    const float4 t = a.ds_in ? __ldg(reinterpret_cast<const float4 *>(a.ds_in) + (c.pt0 + j))
+                             : make_float4(1.f, 1.f, 1.f, 1.f);
     ds[0] = g.pix[0] >= 0 ? t.x : 0.f;
     ds[1] = g.pix[1] >= 0 ? t.y : 0.f;
     ds[2] = g.pix[2] >= 0 ? t.z : 0.f;

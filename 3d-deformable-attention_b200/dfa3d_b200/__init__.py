@@ -11,6 +11,8 @@ from .functions import (  # noqa: F401
     DeformableAttn3DFromOffsetsFunction,
     DeformableAttn3DFromOffsetsFunction_fp32,
     MultiScale3DDeformableAttnFunction,
+    MultiScaleDeformableAttnFunction,
+    MultiScaleDeformableAttnFunction_fp32,
     MultiScale3DDeformableAttnFunction_fp32,
     MultiScaleDepthScoreSampleFunction,
     MultiScaleDepthScoreSampleFunction_fp32,
@@ -25,4 +27,5 @@ __all__ = [
     "MultiScaleDepthScoreSampleFunction_fp32", "WeightedMultiScaleDeformableAttnFunction_fp32",
     "MultiScale3DDeformableAttnFunction_fp32",
     "DeformableAttn3DFromOffsetsFunction", "DeformableAttn3DFromOffsetsFunction_fp32",
+    "MultiScaleDeformableAttnFunction", "MultiScaleDeformableAttnFunction_fp32",
 ]

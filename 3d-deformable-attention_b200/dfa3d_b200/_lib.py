@@ -36,6 +36,8 @@ ENTRY_POINTS = {
     "dfa3d_wms_attn_backward": 12,
     "dfa3d_fused_forward": 9,
     "dfa3d_fused_backward": 12,
+    "dfa3d_msda_forward": 7,
+    "dfa3d_msda_backward": 10,
 }
 # entry points that take `int32_t num_anchors` right after the descriptor
 ENTRY_POINTS_WITH_ANCHORS = {

@@ -180,6 +180,62 @@ def wms_deform_attn_backward(value, value_spatial_shapes, value_level_start_inde
 
 
 # ------------------------------------------------------------------------------------------------
+# plain 2-D multi-scale deformable attention, with the names and signatures of the mmcv extension that
+# BEVFormer_DFA3D's temporal self-attention and decoder call
+# (…/bevformer/modules/multi_scale_deformable_attn_function.py:10-12, :40-46, :74-85)
+# ------------------------------------------------------------------------------------------------
+def ms_deform_attn_forward(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                           attention_weights, im2col_step):
+    """value (B,N,H,C); shapes (L,2); locations (B,Q,H,L,P,2); weights (B,Q,H,L,P) -> (B,Q,H*C)."""
+    _chk(value, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    _chk(value_level_start_index, "level_start_index", _I64)
+    _chk(sampling_locations, "sampling_loc", _F32); _chk(attention_weights, "attn_weight", _F32)
+    _same_device(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                 attention_weights)
+    B, N, H, C = value.shape
+    Bq, Q, Hq, L, P = _loc_dims(sampling_locations, 2)
+    if (Bq, Hq) != (B, H) or tuple(value_spatial_shapes.shape) != (L, 2) \
+            or tuple(attention_weights.shape) != (B, Q, H, L, P):
+        raise RuntimeError("inconsistent shapes between value, spatial_shapes (L,2), sampling_loc and "
+                           "attn_weight")
+    _step_check(B, im2col_step)
+    out = torch.empty((B, Q, H * C), dtype=torch.float32, device=value.device)
+    pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_msda_forward", pr, _ptr(value), _ptr(value_spatial_shapes),
+                  _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(attention_weights),
+                  _ptr(out), _stream(value))
+    return out
+
+
+def ms_deform_attn_backward(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                            attention_weights, grad_output, grad_value, grad_sampling_loc,
+                            grad_attn_weight, im2col_step):
+    """Accumulates into grad_value (float32, caller-zeroed); overwrites the other two."""
+    _chk(value, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    _chk(value_level_start_index, "level_start_index", _I64)
+    _chk(sampling_locations, "sampling_loc", _F32); _chk(attention_weights, "attn_weight", _F32)
+    _chk(grad_output, "grad_output", _F32); _chk(grad_value, "grad_value", _F32)
+    _chk(grad_sampling_loc, "grad_sampling_loc", _F32); _chk(grad_attn_weight, "grad_attn_weight", _F32)
+    _same_device(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                 attention_weights, grad_output, grad_value, grad_sampling_loc, grad_attn_weight)
+    B, N, H, C = value.shape
+    Bq, Q, Hq, L, P = _loc_dims(sampling_locations, 2)
+    if (Bq, Hq) != (B, H) or tuple(value_spatial_shapes.shape) != (L, 2) \
+            or grad_output.numel() != B * Q * H * C or grad_value.shape != value.shape \
+            or grad_sampling_loc.shape != sampling_locations.shape \
+            or grad_attn_weight.shape != attention_weights.shape:
+        raise RuntimeError("inconsistent shapes in ms_deform_attn_backward")
+    _step_check(B, im2col_step)
+    pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_msda_backward", pr, _ptr(value), _ptr(value_spatial_shapes),
+                  _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(attention_weights),
+                  _ptr(grad_output), _ptr(grad_value), _ptr(grad_sampling_loc), _ptr(grad_attn_weight),
+                  _stream(value))
+
+
+# ------------------------------------------------------------------------------------------------
 # one-launch fused entry points (no counterpart in the reference's extension; they serve the
 # one-stage autograd Function)
 # ------------------------------------------------------------------------------------------------

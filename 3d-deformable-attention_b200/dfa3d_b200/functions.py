@@ -112,6 +112,37 @@ class MultiScale3DDeformableAttnFunction(Function):
         return grad_value, grad_dist, None, None, grad_sampling_loc, grad_attn_weight, None, None
 
 
+class MultiScaleDeformableAttnFunction(Function):
+    """Plain 2-D multi-scale deformable attention with the call signature BEVFormer_DFA3D uses for its
+    temporal self-attention and decoder (…/bevformer/modules/multi_scale_deformable_attn_function.py:
+    MultiScaleDeformableAttnFunction_fp32.forward :97-131, backward :133-163; there the kernels come
+    from the third-party mmcv extension).  Here it is the depth-weighted operator with all depth
+    scores 1, on the same kernels."""
+
+    @staticmethod
+    def forward(ctx, value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                attention_weights, im2col_step):
+        ctx.im2col_step = im2col_step
+        output = ext_module.ms_deform_attn_forward(
+            value, value_spatial_shapes, value_level_start_index, sampling_locations, attention_weights,
+            im2col_step=ctx.im2col_step)
+        ctx.save_for_backward(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                              attention_weights)
+        return output
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        value, shapes, lsi, loc, attn = ctx.saved_tensors
+        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_sampling_loc = torch.empty_like(loc)
+        grad_attn_weight = torch.empty_like(attn)
+        ext_module.ms_deform_attn_backward(
+            value, shapes, lsi, loc, attn, grad_output.contiguous(), grad_value, grad_sampling_loc,
+            grad_attn_weight, im2col_step=ctx.im2col_step)
+        return grad_value, None, None, grad_sampling_loc, grad_attn_weight, None
+
+
 class DeformableAttn3DFromOffsetsFunction(Function):
     """The one-stage operator fed with what the attention module's Linear layers produce: reference
     points, raw sampling offsets (pixels / depth bins) and raw attention logits.  The division by the
@@ -160,5 +191,7 @@ WeightedMultiScaleDeformableAttnFunction_fp32 = _fp32_variant(
     WeightedMultiScaleDeformableAttnFunction, "WeightedMultiScaleDeformableAttnFunction_fp32")
 MultiScale3DDeformableAttnFunction_fp32 = _fp32_variant(
     MultiScale3DDeformableAttnFunction, "MultiScale3DDeformableAttnFunction_fp32")
+MultiScaleDeformableAttnFunction_fp32 = _fp32_variant(
+    MultiScaleDeformableAttnFunction, "MultiScaleDeformableAttnFunction_fp32")
 DeformableAttn3DFromOffsetsFunction_fp32 = _fp32_variant(
     DeformableAttn3DFromOffsetsFunction, "DeformableAttn3DFromOffsetsFunction_fp32")

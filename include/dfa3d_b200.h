@@ -116,6 +116,20 @@ int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *
                          const float *attn, const float *grad_out, float *grad_value,
                          float *grad_dist, float *grad_loc3, float *grad_attn, void *stream);
 
+/* Plain 2-D multi-scale deformable attention: the depth-weighted kernels with every depth score 1.
+ * BEVFormer_DFA3D calls this operator (through the third-party mmcv extension, not vendored in the
+ * reference checkout) from its temporal self-attention and decoder,
+ * BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/multi_scale_deformable_attn_function.py:10-12
+ * (ms_deform_attn_forward / ms_deform_attn_backward).  Same layouts as dfa3d_wms_attn_*: shapes2 (L,2),
+ * loc2 (...,2).  grad_value is ACCUMULATED into; grad_loc2 and grad_attn are overwritten. */
+int dfa3d_msda_forward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
+                       const int64_t *level_start, const float *loc2, const float *attn, float *out,
+                       void *stream);
+int dfa3d_msda_backward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
+                        const int64_t *level_start, const float *loc2, const float *attn,
+                        const float *grad_out, float *grad_value, float *grad_loc2, float *grad_attn,
+                        void *stream);
+
 /* The attention module's tensor code folded into the operator.  Replaces, around the one-stage
  * Function, the location assembly and the softmax of MSDeformableAttention3D_DFA3D.forward
  * (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/spatial_cross_attention.py:503-538):

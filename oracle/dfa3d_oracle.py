@@ -196,3 +196,21 @@ def attn3d_backward(value, dist, shapes3, lsi, ref, off_uv, off_d, logits, grad_
     ga = ga.reshape(B, Q, H, L * P)
     g_logits = attn * (ga - (attn * ga).sum(-1, keepdims=True))
     return gv, gd, g_off[..., :2].copy(), g_off[..., 2].copy(), g_logits
+
+
+# ----------------------------------------------------------------------------------------------
+# plain 2-D multi-scale deformable attention = the depth-weighted operator with depth scores 1
+# (call sites: …/bevformer/modules/multi_scale_deformable_attn_function.py:116-122, :147-158)
+# ----------------------------------------------------------------------------------------------
+def ms_deform_attn_forward(value, shapes2, lsi, loc2, attn):
+    value = _c(value)
+    ones = np.ones(tuple(np.asarray(attn).shape) + (4,), dtype=value.dtype)
+    return wms_deform_attn_forward(value, shapes2, lsi, loc2, attn, ones)
+
+
+def ms_deform_attn_backward(value, shapes2, lsi, loc2, attn, grad_out):
+    """Returns (grad_value, grad_loc2, grad_attn)."""
+    value = _c(value)
+    ones = np.ones(tuple(np.asarray(attn).shape) + (4,), dtype=value.dtype)
+    gv, gl, ga, _ = wms_deform_attn_backward(value, shapes2, lsi, loc2, attn, ones, grad_out)
+    return gv, gl, ga

@@ -45,3 +45,23 @@ def dfa3d_grid_sample_grads(value, dist, shapes3, lsi, loc3, attn, grad_out):
     out = dfa3d_grid_sample(leaves[0], leaves[1], shapes3, lsi, leaves[2], leaves[3])
     out.backward(grad_out)
     return (out.detach(),) + tuple(t.grad for t in leaves)
+
+
+def msda_grid_sample(value, shapes2, lsi, loc2, attn):
+    """Plain 2-D multi-scale deformable attention as per-level 4-D ``grid_sample`` -- the published
+    formulation of the operator (mmcv's ``multi_scale_deformable_attn_pytorch``, which the reference
+    calls as its CPU path at BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/
+    temporal_self_attention.py:252 and decoder.py:336; mmcv itself is not part of the reference
+    checkout).  value (B,N,H,C), loc2 (B,Q,H,L,P,2), attn (B,Q,H,L,P) -> (B,Q,H*C)."""
+    B, N, H, C = value.shape
+    _, Q, _, L, P, _ = loc2.shape
+    out = value.new_zeros(B * H, C, Q)
+    for l in range(L):
+        h, w = int(shapes2[l][0]), int(shapes2[l][1])
+        s = int(lsi[l])
+        v = value[:, s:s + h * w].permute(0, 2, 3, 1).reshape(B * H, C, h, w)
+        grid = (2.0 * loc2[:, :, :, l] - 1.0).permute(0, 2, 1, 3, 4).reshape(B * H, Q, P, 2)
+        samp = F.grid_sample(v, grid, mode="bilinear", padding_mode="zeros", align_corners=False)
+        a = attn[:, :, :, l].permute(0, 2, 1, 3).reshape(B * H, 1, Q, P)
+        out = out + (samp * a).sum(-1)
+    return out.view(B, H, C, Q).permute(0, 3, 1, 2).reshape(B, Q, H * C)

@@ -20,7 +20,8 @@ def test_header_declares_the_expected_entry_points():
     names = declared_symbols()
     for n in ("dfa3d_depth_score_forward", "dfa3d_depth_score_backward", "dfa3d_wms_attn_forward",
               "dfa3d_wms_attn_backward", "dfa3d_fused_forward", "dfa3d_fused_backward",
-              "dfa3d_attn3d_forward", "dfa3d_attn3d_backward",
+              "dfa3d_attn3d_forward", "dfa3d_attn3d_backward", "dfa3d_msda_forward",
+              "dfa3d_msda_backward",
               "dfa3d_last_error", "dfa3d_abi_version"):
         assert n in names
 

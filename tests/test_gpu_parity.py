@@ -412,3 +412,26 @@ def test_fp32_variant_casts_under_autocast(M):
     ref16, _ = M.MultiScale3DDeformableAttnFunction.apply(d["value"].half().float(), d["dist"].half().float(),
                                                           d["shapes"], d["lsi"], d["loc"], d["attn"], 64)
     assert torch.equal(out, ref16) and not torch.equal(ref, ref16)
+
+
+@pytest.mark.parametrize("name", ["tiny", "odd", "cfg0"])
+def test_plain_2d_deformable_attention_matches_oracle(M, name):
+    """MultiScaleDeformableAttnFunction (the operator of BEVFormer's temporal self-attention and
+    decoder) on the depth-weighted kernels with depth scores 1."""
+    import dfa3d_oracle as O
+    d = wl.make_inputs(wl.WORKLOADS[name])
+    n = {k: v.numpy() for k, v in d.items()}
+    shapes2 = n["shapes"][:, :2]
+    loc2 = np.ascontiguousarray(n["loc"][..., :2])
+    o = O.ms_deform_attn_forward(n["value"], shapes2, n["lsi"], loc2, n["attn"])
+    gv, gl, ga = O.ms_deform_attn_backward(n["value"], shapes2, n["lsi"], loc2, n["attn"], n["grad_out"])
+    value = d["value"].to(DEV).requires_grad_(True)
+    loc = d["loc"][..., :2].contiguous().to(DEV).requires_grad_(True)
+    attn = d["attn"].to(DEV).requires_grad_(True)
+    out = M.MultiScaleDeformableAttnFunction_fp32.apply(
+        value, d["shapes"][:, :2].contiguous().to(DEV), d["lsi"].to(DEV), loc, attn, 64)
+    out.backward(d["grad_out"].to(DEV))
+    assert_close("out", out, o, **FWD)
+    assert_close("grad_value", value.grad, gv, **BWD)
+    assert_close("grad_loc", loc.grad, gl, **BWD)
+    assert_close("grad_attn", attn.grad, ga, **BWD)

@@ -192,3 +192,22 @@ def test_attn3d_composition_matches_torch_autograd_fp64():
     assert_close("grad_off_uv", guv, n(off_uv.grad), rtol=1e-10, atol=1e-12)
     assert_close("grad_off_d", gdd, n(off_d.grad)[..., 0], rtol=1e-10, atol=1e-12)
     assert_close("grad_logits", glg, n(logits.grad), rtol=1e-10, atol=1e-12)
+
+
+def test_plain_2d_attention_oracle_matches_grid_sample_fp64():
+    import grid_sample_form as G
+    d = wl.make_inputs(wl.WORKLOADS["odd"])
+    dd = {k: (v.double() if v.is_floating_point() else v) for k, v in d.items()}
+    value = dd["value"].clone().requires_grad_(True)
+    loc2 = dd["loc"][..., :2].clone().requires_grad_(True)
+    attn = dd["attn"].clone().requires_grad_(True)
+    out = G.msda_grid_sample(value, dd["shapes"][:, :2].tolist(), dd["lsi"].tolist(), loc2, attn)
+    out.backward(dd["grad_out"])
+    n = lambda t: t.detach().numpy()
+    o = O.ms_deform_attn_forward(n(value), n(dd["shapes"][:, :2]), n(dd["lsi"]), n(loc2), n(attn))
+    gv, gl, ga = O.ms_deform_attn_backward(n(value), n(dd["shapes"][:, :2]), n(dd["lsi"]), n(loc2), n(attn),
+                                           n(dd["grad_out"]))
+    assert_close("out", o, n(out), rtol=1e-11, atol=1e-13)
+    assert_close("grad_value", gv, n(value.grad), rtol=1e-10, atol=1e-12)
+    assert_close("grad_loc", gl, n(loc2.grad), rtol=1e-10, atol=1e-11)
+    assert_close("grad_attn", ga, n(attn.grad), rtol=1e-10, atol=1e-12)
