@@ -38,7 +38,9 @@ import torch.distributed as dist_  # noqa: E402
 NCU_DRAM_TRAFFIC = {
     # profiles/dfa3d_forward_backward_cfg2_2cameras_ncu_full.md: 2-camera capture x 3 (cameras are
     # independent, traffic grows in proportion)
-    "cfg2": {"forward": 3 * (164.730880e6 + 16.864256e6), "backward": 3 * (407.432448e6 + 211.970048e6)},
+    "cfg2": {"forward": 3 * (164.163584e6 + 18.407680e6), "backward": 3 * (409.077760e6 + 212.663808e6)},
+    # profiles/dfa3d_forward_backward_cfg3_bf16_2cameras_ncu_full.md
+    "cfg3": {"forward": 3 * (121.428480e6 + 14.806016e6), "backward": 3 * (242.028032e6 + 142.101504e6)},
 }
 
 
