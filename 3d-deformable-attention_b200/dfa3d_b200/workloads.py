@@ -62,7 +62,9 @@ class Workload:
 _BASE_LEVELS = ((116, 200), (58, 100), (29, 50), (15, 25))
 
 WORKLOADS = {
-    # BASELINE.json configs[0..3]; configs[4] (encoder stack) reuses cfg2's op shapes with D=118.
+    # the benchmark configurations: cfg0 small parity case, cfg1 BEVFormer-small-like single level,
+    # cfg2 BEVFormer-base shape (the headline), cfg3 the same with bf16 storage, cfg4op the operator
+    # shapes of the encoder-stack configuration (D = 118 bins)
     "cfg0": Workload("cfg0", B=1, levels=((32, 32), (16, 16)), D=16, Q=512, P=4, seed=0),
     "cfg1": Workload("cfg1", B=6, levels=((23, 40),), D=64, Q=6000, P=8, seed=1),
     "cfg2": Workload("cfg2", B=6, levels=_BASE_LEVELS, D=64, Q=10000, P=8, seed=2, oob=True),

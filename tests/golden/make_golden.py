@@ -11,7 +11,7 @@ Two sources, both independent of the CUDA kernels under test:
                          against a change of the generator.
 
 Usage:  python tests/golden/make_golden.py --source grid_sample
-        python tests/golden/make_golden.py --source ref_cuda --out gpurun_out/golden
+        python tests/golden/make_golden.py --source ref_cuda --out <dir>   (then copy the .npz files here)
 """
 import argparse
 import hashlib
