@@ -2,7 +2,7 @@
 import numpy as np
 import torch
 
-# Tolerances (stated by the task's north star): forward within 1e-5 relative / 1e-6 absolute in fp32;
+# Acceptance tolerances of this operator: forward within 1e-5 relative / 1e-6 absolute in fp32;
 # backward within 1e-4 relative (atomic reordering); bf16 storage within 1e-2 relative.  Gradients are
 # sums with cancellation, so "relative" is taken against the tensor's scale as well as the element:
 #     |got - ref| <= rtol * |ref| + atol,   atol = atol_frac * max|ref|

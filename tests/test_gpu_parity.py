@@ -104,7 +104,7 @@ def test_shape_coverage_matches_oracle(M, case):
 @pytest.mark.parametrize("case", ["C16", "C32", "C64", "C24_generic"])
 def test_bf16_storage_matches_oracle(M, case):
     """bf16 value/dist, fp32 accumulation and gradients: the oracle consumes the same bf16-rounded
-    numbers in fp32, so the spec's 1e-2 relative bound is met with a wide margin; the fp32-level
+    numbers in fp32, so the 1e-2 relative bound allowed for bf16 storage is met with a wide margin; the fp32-level
     tolerance is what is asserted."""
     C = int(case[1:3])
     w = wl.WORKLOADS["odd"].with_(name=case, C=C, value_dtype="bf16", seed=7)
