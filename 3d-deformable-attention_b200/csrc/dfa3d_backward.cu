@@ -24,7 +24,7 @@ struct PointState {
   PointGeo g;
   float aw;
   float bw[4], ds[4];
-  float lo[4], hi[4];   // depth-distribution values at z0 / z0+1 per corner (fused mode)
+  float dz[4];          // dist[z0+1] - dist[z0] per corner (fused mode): d depth_score / d depth
   bool live;            // j < LP && ok2
 };
 
@@ -34,28 +34,33 @@ __device__ __forceinline__ void bwd_point(const KArgs &a, const LevelTable &lv, 
                                           int (&off)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    s.ds[k] = 0.f; s.bw[k] = 0.f; s.lo[k] = 0.f; s.hi[k] = 0.f; wgt[k] = 0.f; off[k] = -1;
-    s.g.pix[k] = -1;
+    s.ds[k] = 0.f; s.bw[k] = 0.f; s.dz[k] = 0.f; wgt[k] = 0.f; off[k] = -1;
+    s.g.pix[k] = -1; s.g.dpix[k] = -1;
   }
   s.live = false; s.aw = 0.f; s.g.ok2 = false; s.g.ok3 = false;
   if (j >= a.LP) return;
   const int l = j / a.P;
   float x, y, z;
   read_point<MODE>(a, lv, c, j, l, sm, x, y, z, s.aw);
-  s.g = point_geometry(x, y, z, mode_has_depth(MODE), lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N);
+  s.g = point_geometry(x, y, z, mode_has_depth(MODE), lv.h[l], lv.w[l], lv.d[l], lv.start[l], a.N,
+                       dist_map_of(a, lv, l));
   if (!s.g.ok2) return;
   s.live = true;
   bilinear_weights(s.g, s.bw);
   if (mode_has_depth(MODE)) {
     const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
-                        ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
+                        ((long long)c.b * a.Nd * a.dist_pix_stride + c.h * a.dist_head_stride);
     const int Dlim = min(s.g.Dd, a.D);
+    float lo[4], hi[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      load_depth_pair(dist_bh, a.dist_pix_stride, s.g.pix[k], s.g.z0, Dlim, s.g.ok3, s.lo[k], s.hi[k]);
+      load_depth_pair(dist_bh, a.dist_pix_stride, s.g.dpix[k], s.g.z0, Dlim, s.g.ok3, lo[k], hi[k]);
     const float hd = 1.f - s.g.ld;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) s.ds[k] = s.g.ok3 ? s.lo[k] * hd + s.hi[k] * s.g.ld : 0.f;
+    for (int k = 0; k < 4; ++k) {
+      s.ds[k] = s.g.ok3 ? lo[k] * hd + hi[k] * s.g.ld : 0.f;
+      s.dz[k] = hi[k] - lo[k];
+    }
   } else {
     const float4 t = a.ds_in ? __ldg(reinterpret_cast<const float4 *>(a.ds_in) + (c.pt0 + j))
                              : make_float4(1.f, 1.f, 1.f, 1.f);
@@ -97,7 +102,7 @@ __device__ __forceinline__ float bwd_point_epilogue(const KArgs &a, const ItemCt
     g_x = (float)s.g.W * s.aw * (hh * (e1 - e0) + s.g.lh * (e2 - e3));
     g_y = (float)s.g.Hh * s.aw * (hw * (e3 - e0) + s.g.lw * (e2 - e1));
     if (mode_has_depth(MODE) && s.g.ok3) {
-      float *gd_bh = a.grad_dist + ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
+      float *gd_bh = a.grad_dist + ((long long)c.b * a.Nd * a.dist_pix_stride + c.h * a.dist_head_stride);
       const float hd = 1.f - s.g.ld;
       const int Dlim = min(s.g.Dd, a.D);
       float acc = 0.f;
@@ -105,9 +110,9 @@ __device__ __forceinline__ float bwd_point_epilogue(const KArgs &a, const ItemCt
       for (int k = 0; k < 4; ++k) {
         if (s.g.pix[k] >= 0) {
           if (gds[k] != 0.f)
-            red_depth_pair(gd_bh, a.dist_pix_stride, s.g.pix[k], s.g.z0, Dlim, a.D, hd * gds[k],
+            red_depth_pair(gd_bh, a.dist_pix_stride, s.g.dpix[k], s.g.z0, Dlim, a.D, hd * gds[k],
                            s.g.ld * gds[k]);
-          acc = fmaf(gds[k], s.hi[k] - s.lo[k], acc);
+          acc = fmaf(gds[k], s.dz[k], acc);
         }
       }
       g_z = (float)s.g.Dd * acc;
@@ -150,32 +155,52 @@ __device__ __forceinline__ void finish_logit_grads(const KArgs &a, const ItemCtx
 // ------------------------------------------------------------------------------------------------
 // fused / given-depth-score backward, C/4 a power of two
 // ------------------------------------------------------------------------------------------------
-// fp32 value: 4 CTAs (32 warps) per SM is the measured optimum (64 registers, a few bytes of spill);
-// bf16 value carries twice the channels per lane and would spill heavily under that cap.
-template <typename VT> constexpr int backward_min_ctas() { return 4; }
+// Dot products of U = 4 row fragments with the grad_out fragment, summed over the G lanes of a group.
+// For G = 8 the four sums are folded together: after the first exchange a lane keeps two of them, after
+// the second one, so the whole reduction takes 4 shuffles instead of 12 and lane `sub` < 4 of every
+// group ends up with the total of row u = 2*(sub & 1) + ((sub >> 1) & 1).  Shuffles travel through the
+// same pipe as the shared-memory and global accesses this kernel is bound by.
+// Returns the lane's total and, in `u_mine`, which of the four rows it belongs to (-1: none).
+template <int G>
+__device__ __forceinline__ float fold_four_dots(const float (&d)[4], int sub, int &u_mine) {
+  if (G == 8) {
+    const bool b0 = sub & 1, b1 = sub & 2;
+    const float r0 = __shfl_xor_sync(0xffffffffu, b0 ? d[0] : d[2], 1);
+    const float r1 = __shfl_xor_sync(0xffffffffu, b0 ? d[1] : d[3], 1);
+    const float e0 = (b0 ? d[2] : d[0]) + r0, e1 = (b0 ? d[3] : d[1]) + r1;
+    const float r2 = __shfl_xor_sync(0xffffffffu, b1 ? e0 : e1, 2);
+    float f = (b1 ? e1 : e0) + r2;
+    f += __shfl_xor_sync(0xffffffffu, f, 4);
+    u_mine = sub < 4 ? (b0 ? 2 : 0) + (b1 ? 1 : 0) : -1;
+    return f;
+  }
+  // other group widths (G = 4, 16, 32): one butterfly per row, lane u of the group keeps row u
+  float mine = 0.f;
+  u_mine = -1;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    float t = d[u];
+#pragma unroll
+    for (int s = 1; s < G; s <<= 1) t += __shfl_xor_sync(0xffffffffu, t, s);
+    if (sub == u) { mine = t; u_mine = u; }
+  }
+  return mine;
+}
 
+// One item of the backward: `table` / `dot_slots` are the warp's slices of shared memory.
 template <typename VT, typename DT, int C, int MODE, bool FULL>
-__global__ void __launch_bounds__(kThreads, backward_min_ctas<VT>())
-dfa3d_backward_kernel(const KArgs a) {
+__device__ __forceinline__ void backward_item(const KArgs &a, const LevelTable &lv, const ItemCtx &c,
+                                              RowEntry *table, float *dot_slots, int lane) {
   constexpr int V = RowVec4<VT>::kElems;
   constexpr int G = C / V;
   constexpr int R = 32 / G;
   constexpr int U = 4;
-
-  __shared__ LevelTable lv;
-  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
-  __shared__ __align__(16) float dots[kWarpsPerCta][128];
-  stage_levels(lv, a);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  ItemCtx c;
-  if (!item_context(a, warp, c)) return;
   const int sub = lane % G, grp = lane / G;
   const long long slice = ((long long)c.b * a.N * a.H + c.h) * C + sub * V;
   const VT *vbase = reinterpret_cast<const VT *>(a.value) + slice;
   float *gvbase = a.grad_value + slice;
-  const RowEntry *my = rows[warp] + grp;
-  float *myd = dots[warp] + grp;
+  const RowEntry *my = table + grp;
+  float *myd = dot_slots + grp;
 
   float go[V];
   {
@@ -196,7 +221,7 @@ dfa3d_backward_kernel(const KArgs a) {
     float wgt[4];
     int off[4];
     bwd_point<DT, MODE>(a, lv, c, chunk + lane, sm, st, wgt, off);
-    store_rows(rows[warp], lane, off, wgt);
+    store_rows(table, lane, off, wgt);
     __syncwarp();
     auto step = [&](int r0, int nrows) {
       RowEntry e[U];
@@ -215,15 +240,31 @@ dfa3d_backward_kernel(const KArgs a) {
           for (int i = 0; i < V; ++i) v[u][i] = 0.f;
         }
       }
+      float d[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        float d = 0.f;
+        d[u] = 0.f;
 #pragma unroll
-        for (int i = 0; i < V; ++i) d = fmaf(v[u][i], go[i], d);
+        for (int i = 0; i < V; ++i) d[u] = fmaf(v[u][i], go[i], d[u]);
+      }
+      if (G >= 4) {
+        int u_mine;
+        const float f = fold_four_dots<G>(d, sub, u_mine);
+        const int r = r0 + u_mine * R;
+        if (u_mine >= 0 && (FULL || r + grp < nrows)) myd[r] = f;
+      } else {
+        // groups of 2 lanes (8 channels): a group's first lane stores its four totals one by one
 #pragma unroll
-        for (int s = 1; s < G; s <<= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
-        const int r = r0 + u * R;
-        if (sub == 0 && (FULL || r + grp < nrows)) myd[r] = d;
+        for (int u = 0; u < U; ++u) {
+          float t = d[u];
+#pragma unroll
+          for (int s = 1; s < G; s <<= 1) t += __shfl_xor_sync(0xffffffffu, t, s);
+          const int r = r0 + u * R;
+          if (sub == 0 && (FULL || r + grp < nrows)) myd[r] = t;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
         if (e[u].off >= 0 && e[u].wgt != 0.f) {
           float *gp = gvbase + e[u].off;
 #pragma unroll
@@ -237,12 +278,33 @@ dfa3d_backward_kernel(const KArgs a) {
 #pragma unroll 1
     for (int r0 = 0; r0 < nrows; r0 += R * U) step(r0, nrows);
     __syncwarp();
-    const float4 tq = reinterpret_cast<const float4 *>(dots[warp])[lane];
+    const float4 tq = reinterpret_cast<const float4 *>(dot_slots)[lane];
     const float t[4] = {tq.x, tq.y, tq.z, tq.w};
     dot += bwd_point_epilogue<DT, MODE>(a, c, chunk + lane, st, t);
     __syncwarp();
   }
   if (MODE == kCallerFused) finish_logit_grads(a, c, lane, sm, dot);
+}
+
+// ------------------------------------------------------------------------------------------------
+// fused / given-depth-score backward, C/4 a power of two
+// ------------------------------------------------------------------------------------------------
+// 4 CTAs (32 warps) per SM is the measured optimum (64 registers, a few bytes of spill); a CTA walks
+// DFA3D_BWD_ITEMS_PER_WARP consecutive groups of 8 items before it retires.
+template <typename VT, typename DT, int C, int MODE, bool FULL>
+__global__ void __launch_bounds__(kThreads, DFA3D_BWD_MIN_CTAS)
+dfa3d_backward_kernel(const KArgs a) {
+  __shared__ LevelTable lv;
+  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
+  __shared__ __align__(16) float dots[kWarpsPerCta][128];
+  stage_levels(lv, a);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll 1
+  for (int it = 0; it < DFA3D_BWD_ITEMS_PER_WARP; ++it) {
+    ItemCtx c;
+    if (!item_context(a, warp, blockIdx.x * DFA3D_BWD_ITEMS_PER_WARP + it, c)) return;
+    backward_item<VT, DT, C, MODE, FULL>(a, lv, c, rows[warp], dots[warp], lane);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -257,7 +319,7 @@ dfa3d_backward_generic_kernel(const KArgs a) {
   stage_levels(lv, a);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   ItemCtx c;
-  if (!item_context(a, warp, c)) return;
+  if (!item_context(a, warp, blockIdx.x, c)) return;
   const int C = a.C;
   const long long slice = ((long long)c.b * a.N * a.H + c.h) * C;
   const VT *vbase = reinterpret_cast<const VT *>(a.value) + slice;
@@ -317,10 +379,10 @@ dfa3d_depth_score_backward_kernel(const KArgs a) {
     const int b = (int)(item / a.items_per_cam);
     const float *lp = a.loc + pt * 3;
     const PointGeo g = point_geometry(__ldg(lp), __ldg(lp + 1), __ldg(lp + 2), true, lv.h[l], lv.w[l],
-                                      lv.d[l], lv.start[l], a.N);
+                                      lv.d[l], lv.start[l], a.N, dist_map_of(a, lv, l));
     float g_z = 0.f;
     if (g.ok3) {
-      const long long bh = (long long)b * a.N * a.dist_pix_stride + h * a.dist_head_stride;
+      const long long bh = (long long)b * a.Nd * a.dist_pix_stride + h * a.dist_head_stride;
       const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) + bh;
       float *gd_bh = a.grad_dist + bh;
       const float4 gq = __ldg(reinterpret_cast<const float4 *>(a.grad_ds_in) + pt);
@@ -332,8 +394,8 @@ dfa3d_depth_score_backward_kernel(const KArgs a) {
       for (int k = 0; k < 4; ++k) {
         if (g.pix[k] >= 0) {
           float lo, hi;
-          load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, Dlim, true, lo, hi);
-          red_depth_pair(gd_bh, a.dist_pix_stride, g.pix[k], g.z0, Dlim, a.D, hd * gds[k], g.ld * gds[k]);
+          load_depth_pair(dist_bh, a.dist_pix_stride, g.dpix[k], g.z0, Dlim, true, lo, hi);
+          red_depth_pair(gd_bh, a.dist_pix_stride, g.dpix[k], g.z0, Dlim, a.D, hd * gds[k], g.ld * gds[k]);
           acc = fmaf(gds[k], hi - lo, acc);
         }
       }
@@ -355,7 +417,11 @@ static void launch_backward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
     case 4:  dfa3d_backward_kernel<VT, DT, 4 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 8:  dfa3d_backward_kernel<VT, DT, 8 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 16: dfa3d_backward_kernel<VT, DT, 16 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
-    default: dfa3d_backward_generic_kernel<VT, DT, MODE><<<grid, kThreads, 0, s>>>(a); break;
+    default: {
+      const dim3 g1((unsigned)((a.items_per_cam + kWarpsPerCta - 1) / kWarpsPerCta), grid.y, 1);
+      dfa3d_backward_generic_kernel<VT, DT, MODE><<<g1, kThreads, 0, s>>>(a);
+      break;
+    }
   }
 }
 
@@ -365,7 +431,8 @@ static cudaError_t launch_backward_vd(const KArgs &a0, cudaStream_t s) {
   for (int b0 = 0; b0 < a0.B; b0 += 65535) {      // grid.y limit
     KArgs a = a0;
     a.b0 = b0;
-    const dim3 grid((unsigned)((a.items_per_cam + kWarpsPerCta - 1) / kWarpsPerCta),
+    constexpr int kPerCta = kWarpsPerCta * DFA3D_BWD_ITEMS_PER_WARP;
+    const dim3 grid((unsigned)((a.items_per_cam + kPerCta - 1) / kPerCta),
                     (unsigned)min(65535, a0.B - b0), 1);
     if (full) launch_backward_g<VT, DT, MODE, true>(a, grid, s);
     else launch_backward_g<VT, DT, MODE, false>(a, grid, s);

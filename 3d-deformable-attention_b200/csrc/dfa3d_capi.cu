@@ -51,8 +51,12 @@ int check_problem(const dfa3d_problem *p, bool need_value, bool need_dist) {
     if (p->dist_head_stride != 0 && p->dist_head_stride != p->D)
       return fail(DFA3D_ERR_INVALID_ARGUMENT, "dist_head_stride must be 0 (shared) or D (per head), got %lld",
                   (long long)p->dist_head_stride);
-    if ((long long)p->N * p->H * p->D >= (1LL << 31))
-      return fail(DFA3D_ERR_UNSUPPORTED, "N*H*D must stay below 2^31 (one camera's dist slice)");
+    if ((p->dist_map_h > 0) != (p->dist_map_w > 0) || p->dist_map_h < 0 || p->dist_map_w < 0)
+      return fail(DFA3D_ERR_INVALID_ARGUMENT, "dist_map_h and dist_map_w must both be 0 or both positive "
+                  "(got %d, %d)", p->dist_map_h, p->dist_map_w);
+    const long long rows = p->dist_map_h > 0 ? (long long)p->dist_map_h * p->dist_map_w : p->N;
+    if (rows * p->H * p->D >= (1LL << 31))
+      return fail(DFA3D_ERR_UNSUPPORTED, "rows*H*D of one camera's dist slice must stay below 2^31");
   }
   return DFA3D_OK;
 }
@@ -77,6 +81,8 @@ dfa3d::KArgs base_args(const dfa3d_problem *p, int shape_stride, int loc_stride)
   a.items_per_cam = p->Q * p->H;
   a.dist_head_stride = (int)p->dist_head_stride;
   a.dist_pix_stride = p->dist_head_stride == 0 ? p->D : p->H * p->D;
+  a.dmap_h = p->dist_map_h; a.dmap_w = p->dist_map_w;
+  a.Nd = p->dist_map_h > 0 ? p->dist_map_h * p->dist_map_w : p->N;
   return a;
 }
 
@@ -162,9 +168,10 @@ int dfa3d_wms_attn_backward(const dfa3d_problem *p, const void *value, const int
                 "dfa3d_wms_attn_backward launch");
 }
 
-int dfa3d_fused_forward(const dfa3d_problem *p, const void *value, const void *dist,
-                        const int64_t *shapes3, const int64_t *level_start, const float *loc3,
-                        const float *attn, float *out, float *depth_score_out, void *stream) {
+static int fused_forward_impl(const dfa3d_problem *p, const int32_t *query_offsets, const void *value,
+                              const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                              const float *loc3, const float *attn, float *out, float *depth_score_out,
+                              void *stream) {
   if (int rc = check_problem(p, true, true)) return rc;
   if (p->B == 0 || p->Q == 0) return DFA3D_OK;
   REQUIRE_PTR(value); REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start);
@@ -172,17 +179,34 @@ int dfa3d_fused_forward(const dfa3d_problem *p, const void *value, const void *d
   REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(out); REQUIRE_ALIGNED(depth_score_out);
   dfa3d::KArgs a = base_args(p, 3, 3);
   a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
-  a.attn = attn; a.out = out; a.ds_out = depth_score_out;
+  a.attn = attn; a.out = out; a.ds_out = depth_score_out; a.q_off = query_offsets;
   return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16,
                                       p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kFused,
                                       (cudaStream_t)stream),
                 "dfa3d_fused_forward launch");
 }
 
-int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *dist,
-                         const int64_t *shapes3, const int64_t *level_start, const float *loc3,
-                         const float *attn, const float *grad_out, float *grad_value,
-                         float *grad_dist, float *grad_loc3, float *grad_attn, void *stream) {
+int dfa3d_fused_forward(const dfa3d_problem *p, const void *value, const void *dist,
+                        const int64_t *shapes3, const int64_t *level_start, const float *loc3,
+                        const float *attn, float *out, float *depth_score_out, void *stream) {
+  return fused_forward_impl(p, nullptr, value, dist, shapes3, level_start, loc3, attn, out,
+                            depth_score_out, stream);
+}
+
+int dfa3d_fused_forward_ragged(const dfa3d_problem *p, const int32_t *query_offsets, const void *value,
+                               const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                               const float *loc3, const float *attn, float *out,
+                               float *depth_score_out, void *stream) {
+  REQUIRE_PTR(query_offsets);
+  return fused_forward_impl(p, query_offsets, value, dist, shapes3, level_start, loc3, attn, out,
+                            depth_score_out, stream);
+}
+
+static int fused_backward_impl(const dfa3d_problem *p, const int32_t *query_offsets, const void *value,
+                               const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                               const float *loc3, const float *attn, const float *grad_out,
+                               float *grad_value, float *grad_dist, float *grad_loc3, float *grad_attn,
+                               void *stream) {
   if (int rc = check_problem(p, true, true)) return rc;
   if (p->B == 0 || p->Q == 0) return DFA3D_OK;
   REQUIRE_PTR(value); REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start);
@@ -192,11 +216,29 @@ int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *
   dfa3d::KArgs a = base_args(p, 3, 3);
   a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
   a.attn = attn; a.grad_out = grad_out; a.grad_value = grad_value; a.grad_dist = grad_dist;
-  a.grad_loc = grad_loc3; a.grad_attn = grad_attn;
+  a.grad_loc = grad_loc3; a.grad_attn = grad_attn; a.q_off = query_offsets;
   return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16,
                                        p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kFused,
                                        (cudaStream_t)stream),
                 "dfa3d_fused_backward launch");
+}
+
+int dfa3d_fused_backward(const dfa3d_problem *p, const void *value, const void *dist,
+                         const int64_t *shapes3, const int64_t *level_start, const float *loc3,
+                         const float *attn, const float *grad_out, float *grad_value,
+                         float *grad_dist, float *grad_loc3, float *grad_attn, void *stream) {
+  return fused_backward_impl(p, nullptr, value, dist, shapes3, level_start, loc3, attn, grad_out,
+                             grad_value, grad_dist, grad_loc3, grad_attn, stream);
+}
+
+int dfa3d_fused_backward_ragged(const dfa3d_problem *p, const int32_t *query_offsets, const void *value,
+                                const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                                const float *loc3, const float *attn, const float *grad_out,
+                                float *grad_value, float *grad_dist, float *grad_loc3,
+                                float *grad_attn, void *stream) {
+  REQUIRE_PTR(query_offsets);
+  return fused_backward_impl(p, query_offsets, value, dist, shapes3, level_start, loc3, attn, grad_out,
+                             grad_value, grad_dist, grad_loc3, grad_attn, stream);
 }
 
 int dfa3d_msda_forward(const dfa3d_problem *p, const void *value, const int64_t *shapes2,
@@ -232,10 +274,12 @@ int dfa3d_msda_backward(const dfa3d_problem *p, const void *value, const int64_t
                 "dfa3d_msda_backward launch");
 }
 
-int dfa3d_attn3d_forward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
-                         const void *dist, const int64_t *shapes3, const int64_t *level_start,
-                         const float *ref_points, const float *offsets_uv, const float *offsets_depth,
-                         const float *logits, float *out, void *stream) {
+static int attn3d_forward_impl(const dfa3d_problem *p, int32_t num_anchors,
+                               const int32_t *query_offsets, const void *value, const void *dist,
+                               const int64_t *shapes3, const int64_t *level_start,
+                               const float *ref_points, const float *offsets_uv,
+                               const float *offsets_depth, const float *logits, float *out,
+                               void *stream) {
   if (int rc = check_problem(p, true, true)) return rc;
   if (num_anchors <= 0 || p->P % num_anchors != 0)
     return fail(DFA3D_ERR_INVALID_ARGUMENT, "num_anchors=%d must be positive and divide P=%d",
@@ -248,18 +292,39 @@ int dfa3d_attn3d_forward(const dfa3d_problem *p, int32_t num_anchors, const void
   dfa3d::KArgs a = base_args(p, 3, 3);
   a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.ref = ref_points;
   a.off_uv = offsets_uv; a.off_d = offsets_depth; a.logits = logits; a.Z = num_anchors; a.out = out;
+  a.q_off = query_offsets;
   return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16,
                                       p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kCallerFused,
                                       (cudaStream_t)stream),
                 "dfa3d_attn3d_forward launch");
 }
 
-int dfa3d_attn3d_backward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
-                          const void *dist, const int64_t *shapes3, const int64_t *level_start,
-                          const float *ref_points, const float *offsets_uv,
-                          const float *offsets_depth, const float *logits, const float *grad_out,
-                          float *grad_value, float *grad_dist, float *grad_offsets_uv,
-                          float *grad_offsets_depth, float *grad_logits, void *stream) {
+int dfa3d_attn3d_forward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
+                         const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                         const float *ref_points, const float *offsets_uv, const float *offsets_depth,
+                         const float *logits, float *out, void *stream) {
+  return attn3d_forward_impl(p, num_anchors, nullptr, value, dist, shapes3, level_start, ref_points,
+                             offsets_uv, offsets_depth, logits, out, stream);
+}
+
+int dfa3d_attn3d_forward_ragged(const dfa3d_problem *p, int32_t num_anchors,
+                                const int32_t *query_offsets, const void *value, const void *dist,
+                                const int64_t *shapes3, const int64_t *level_start,
+                                const float *ref_points, const float *offsets_uv,
+                                const float *offsets_depth, const float *logits, float *out,
+                                void *stream) {
+  REQUIRE_PTR(query_offsets);
+  return attn3d_forward_impl(p, num_anchors, query_offsets, value, dist, shapes3, level_start, ref_points,
+                             offsets_uv, offsets_depth, logits, out, stream);
+}
+
+static int attn3d_backward_impl(const dfa3d_problem *p, int32_t num_anchors,
+                                const int32_t *query_offsets, const void *value, const void *dist,
+                                const int64_t *shapes3, const int64_t *level_start,
+                                const float *ref_points, const float *offsets_uv,
+                                const float *offsets_depth, const float *logits, const float *grad_out,
+                                float *grad_value, float *grad_dist, float *grad_offsets_uv,
+                                float *grad_offsets_depth, float *grad_logits, void *stream) {
   if (int rc = check_problem(p, true, true)) return rc;
   if (num_anchors <= 0 || p->P % num_anchors != 0)
     return fail(DFA3D_ERR_INVALID_ARGUMENT, "num_anchors=%d must be positive and divide P=%d",
@@ -275,10 +340,81 @@ int dfa3d_attn3d_backward(const dfa3d_problem *p, int32_t num_anchors, const voi
   a.off_uv = offsets_uv; a.off_d = offsets_depth; a.logits = logits; a.Z = num_anchors;
   a.grad_out = grad_out; a.grad_value = grad_value; a.grad_dist = grad_dist;
   a.grad_off_uv = grad_offsets_uv; a.grad_off_d = grad_offsets_depth; a.grad_logits = grad_logits;
+  a.q_off = query_offsets;
   return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16,
                                        p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kCallerFused,
                                        (cudaStream_t)stream),
                 "dfa3d_attn3d_backward launch");
+}
+
+int dfa3d_attn3d_backward(const dfa3d_problem *p, int32_t num_anchors, const void *value,
+                          const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                          const float *ref_points, const float *offsets_uv,
+                          const float *offsets_depth, const float *logits, const float *grad_out,
+                          float *grad_value, float *grad_dist, float *grad_offsets_uv,
+                          float *grad_offsets_depth, float *grad_logits, void *stream) {
+  return attn3d_backward_impl(p, num_anchors, nullptr, value, dist, shapes3, level_start, ref_points,
+                              offsets_uv, offsets_depth, logits, grad_out, grad_value, grad_dist,
+                              grad_offsets_uv, grad_offsets_depth, grad_logits, stream);
+}
+
+int dfa3d_attn3d_backward_ragged(const dfa3d_problem *p, int32_t num_anchors,
+                                 const int32_t *query_offsets, const void *value, const void *dist,
+                                 const int64_t *shapes3, const int64_t *level_start,
+                                 const float *ref_points, const float *offsets_uv,
+                                 const float *offsets_depth, const float *logits, const float *grad_out,
+                                 float *grad_value, float *grad_dist, float *grad_offsets_uv,
+                                 float *grad_offsets_depth, float *grad_logits, void *stream) {
+  REQUIRE_PTR(query_offsets);
+  return attn3d_backward_impl(p, num_anchors, query_offsets, value, dist, shapes3, level_start,
+                              ref_points, offsets_uv, offsets_depth, logits, grad_out, grad_value,
+                              grad_dist, grad_offsets_uv, grad_offsets_depth, grad_logits, stream);
+}
+
+// ---- per-camera re-batching -----------------------------------------------------------------
+int dfa3d_rebatch_plan(const uint8_t *bev_mask, int32_t cams, int32_t bs, int32_t Q, int32_t Z,
+                       int32_t *counts, int32_t *offsets, int32_t *op_offsets, int32_t *packed_query,
+                       int32_t *packed_camera, int32_t *row_of, float *inv_count, void *stream) {
+  if (cams <= 0 || bs <= 0 || Q < 0 || Z <= 0)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "cams, bs, Z must be positive and Q >= 0 (got %d %d %d %d)",
+                cams, bs, Z, Q);
+  if ((long long)cams * Q >= (1LL << 31) || (long long)bs * cams * Q >= (1LL << 31))
+    return fail(DFA3D_ERR_UNSUPPORTED, "bs * cams * Q must stay below 2^31");
+  REQUIRE_PTR(counts); REQUIRE_PTR(offsets); REQUIRE_PTR(op_offsets); REQUIRE_PTR(packed_query);
+  REQUIRE_PTR(packed_camera); REQUIRE_PTR(row_of); REQUIRE_PTR(inv_count);
+  if (Q > 0) REQUIRE_PTR(bev_mask);
+  return finish(dfa3d::launch_rebatch_plan(bev_mask, cams, bs, Q, Z, counts, offsets, op_offsets,
+                                           packed_query, packed_camera, row_of, inv_count,
+                                           (cudaStream_t)stream),
+                "dfa3d_rebatch_plan launch");
+}
+
+int dfa3d_rebatch_gather(const float *src, const int32_t *packed_query, const int32_t *packed_camera,
+                         const int32_t *offsets, int32_t cams, int32_t bs, int32_t Q, int32_t width,
+                         int64_t src_camera_stride, int64_t src_batch_stride, const float *scale,
+                         float *dst, int64_t rows_bound, void *stream) {
+  if (cams <= 0 || bs <= 0 || Q < 0 || width <= 0 || rows_bound < 0 || src_camera_stride < 0 ||
+      src_batch_stride < 0)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "dfa3d_rebatch_gather: bad size");
+  if (rows_bound == 0) return DFA3D_OK;
+  REQUIRE_PTR(src); REQUIRE_PTR(packed_query); REQUIRE_PTR(packed_camera); REQUIRE_PTR(offsets);
+  REQUIRE_PTR(dst);
+  return finish(dfa3d::launch_rebatch_gather(src, packed_query, packed_camera, offsets, cams, bs, Q, width,
+                                             src_camera_stride, src_batch_stride, scale, dst, rows_bound,
+                                             (cudaStream_t)stream),
+                "dfa3d_rebatch_gather launch");
+}
+
+int dfa3d_rebatch_combine(const float *src, const int32_t *row_of, const int32_t *offsets, int32_t cams,
+                          int32_t bs, int32_t Q, int32_t width, const float *scale, float *dst,
+                          void *stream) {
+  if (cams <= 0 || bs <= 0 || Q < 0 || width <= 0)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "dfa3d_rebatch_combine: bad size");
+  if (Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(src); REQUIRE_PTR(row_of); REQUIRE_PTR(offsets); REQUIRE_PTR(dst);
+  return finish(dfa3d::launch_rebatch_combine(src, row_of, offsets, cams, bs, Q, width, scale, dst,
+                                              (cudaStream_t)stream),
+                "dfa3d_rebatch_combine launch");
 }
 
 }  // extern "C"

@@ -33,6 +33,23 @@ __host__ __device__ constexpr bool mode_has_depth(int m) { return m != kGivenDep
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
 
+// Compile-time tuning knobs (defaults = the measured optimum on B200 at the BEVFormer-base shape).
+//   *_ITEMS_PER_WARP  consecutive CTA-sized groups of items a CTA works through before it retires:
+//                     fewer, longer-lived CTAs (a CTA that handles one item per warp lives ~2 us)
+//   *_MIN_CTAS        __launch_bounds__ residency target, i.e. the register cap
+#ifndef DFA3D_FWD_ITEMS_PER_WARP
+#define DFA3D_FWD_ITEMS_PER_WARP 8
+#endif
+#ifndef DFA3D_BWD_ITEMS_PER_WARP
+#define DFA3D_BWD_ITEMS_PER_WARP 4
+#endif
+#ifndef DFA3D_FWD_MIN_CTAS
+#define DFA3D_FWD_MIN_CTAS 5
+#endif
+#ifndef DFA3D_BWD_MIN_CTAS
+#define DFA3D_BWD_MIN_CTAS 4
+#endif
+
 // Kernel argument block (device pointers + sizes).  Unused pointers are null.
 struct KArgs {
   const void *value;       // (B,N,H,C) fp32|bf16
@@ -52,6 +69,9 @@ struct KArgs {
   float *grad_off_d;       // (B,Q,H,L,P), overwritten
   float *grad_logits;      // (B,Q,H,L*P), overwritten
   int Z;                   // reference points (pillar anchors) per query
+  // ragged queries: camera b owns the packed query rows [q_off[b], q_off[b+1]) of every per-query
+  // tensor; Q is then only the bound the grid is sized for.  Null = every camera has Q queries.
+  const int32_t *q_off;
   const float *grad_ds_in; // (B,Q,H,L,P,4) incoming depth-score gradient (two-stage depth backward)
   float *out;              // (B,Q,H*C)
   float *ds_out;           // (B,Q,H,L,P,4) or null
@@ -69,11 +89,15 @@ struct KArgs {
   long long items;         // B*Q*H
   int dist_pix_stride;     // elements between pixels of dist: H*D or D
   int dist_head_stride;    // D or 0
+  int Nd;                  // rows of dist per camera: N, or dmap_h * dmap_w
+  int dmap_h, dmap_w;      // > 0: dist is one dmap_h x dmap_w map per camera, read by every level with
+                           // nearest-neighbour indexing (F.interpolate(mode="nearest") semantics)
 };
 
 // Level table staged in shared memory once per CTA.
 struct LevelTable {
   int h[kMaxLevels], w[kMaxLevels], d[kMaxLevels], start[kMaxLevels];
+  float map_sy[kMaxLevels], map_sx[kMaxLevels];   // dist map: (float)map size / level size per axis
 };
 
 __device__ __forceinline__ void stage_levels(LevelTable &t, const KArgs &a) {
@@ -82,6 +106,9 @@ __device__ __forceinline__ void stage_levels(LevelTable &t, const KArgs &a) {
     t.w[l] = (int)a.shapes[l * a.shape_stride + 1];
     t.d[l] = a.shape_stride == 3 ? (int)a.shapes[l * 3 + 2] : a.D;
     t.start[l] = (int)a.lsi[l];
+    // the resize's scale, formed in fp32 from the two sizes as torch's nearest interpolation forms it
+    t.map_sy[l] = a.dmap_h > 0 ? (float)a.dmap_h / (float)t.h[l] : 1.f;
+    t.map_sx[l] = a.dmap_w > 0 ? (float)a.dmap_w / (float)t.w[l] : 1.f;
   }
   __syncthreads();
 }
@@ -97,16 +124,24 @@ struct ItemCtx {
   long long pt0;            // index of the item's first point: item * LP
 };
 
-// blockIdx.y (+ b0) selects the camera, blockIdx.x * warps + warp the (query, head) pair inside it.
-// Returns false for the warps past the end of the camera.
-__device__ __forceinline__ bool item_context(const KArgs &a, int warp, ItemCtx &c) {
-  const unsigned idx = blockIdx.x * kWarpsPerCta + warp;
+// blockIdx.y (+ b0) selects the camera; the CTA's `group`-th group of kWarpsPerCta items starts at
+// (blockIdx.x * groups_per_cta + group) * kWarpsPerCta, warp w takes item w of it: a (query, head)
+// pair of that camera.  Returns false for the warps past the end of the camera.
+__device__ __forceinline__ bool item_context(const KArgs &a, int warp, unsigned group, ItemCtx &c) {
+  const unsigned idx = group * kWarpsPerCta + warp;
   if (idx >= (unsigned)a.items_per_cam) return false;
   c.b = (int)blockIdx.y + a.b0;
   const unsigned q = idx / (unsigned)a.H;
   c.h = (int)(idx - q * (unsigned)a.H);
-  c.bq = (long long)c.b * a.Q + q;
-  c.item = (long long)c.b * a.items_per_cam + idx;
+  if (a.q_off) {
+    const int q0 = __ldg(a.q_off + c.b);
+    if ((int)q >= __ldg(a.q_off + c.b + 1) - q0) return false;
+    c.bq = (long long)q0 + q;
+    c.item = c.bq * a.H + c.h;
+  } else {
+    c.bq = (long long)c.b * a.Q + q;
+    c.item = (long long)c.b * a.items_per_cam + idx;
+  }
   c.pt0 = c.item * a.LP;
   c.loc = a.loc + c.pt0 * a.loc_stride;      // (not dereferenced in caller-fused mode)
   c.attn = a.attn + c.pt0;
@@ -161,6 +196,7 @@ __device__ __forceinline__ void read_point(const KArgs &a, const LevelTable &lv,
 struct PointGeo {
   float lw, lh, ld;   // fractional parts; hw = 1-lw etc.
   int pix[4];         // pixel index inside the camera (level start included), -1 if corner k unusable
+  int dpix[4];        // row of dist that belongs to corner k (== pix[k] unless dist is a single map)
   int z0;             // lower depth bin (may be -1); upper = z0+1
   int W, Hh, Dd;
   bool ok2, ok3;
@@ -169,8 +205,25 @@ struct PointGeo {
 // `has_z`: the location carries a depth coordinate (3-D range test applies to ok3).
 // Corner pixels are additionally bounded by N so that inconsistent shape tables cannot make the
 // kernels touch memory outside the tensors (such corners are treated as outside the image).
+// Row of the dist map that pixel (y, x) of a level reads: nearest-neighbour resize,
+// src = min(floor(dst * scale), size - 1) with scale = (float)map size / (float)level size.
+__device__ __forceinline__ int map_row(int y, int x, float sy, float sx, int mh, int mw) {
+  const int my = min((int)floorf((float)y * sy), mh - 1);
+  const int mx = min((int)floorf((float)x * sx), mw - 1);
+  return my * mw + mx;
+}
+
+struct DistMap {
+  int h, w;           // 0, 0: dist is laid out like value
+  float sy, sx;
+};
+__device__ __forceinline__ DistMap dist_map_of(const KArgs &a, const LevelTable &lv, int l) {
+  return DistMap{a.dmap_h, a.dmap_w, lv.map_sy[l], lv.map_sx[l]};
+}
+
 __device__ __forceinline__ PointGeo point_geometry(float x, float y, float z, bool has_z, int Hh,
-                                                   int W, int Dd, int start, int N) {
+                                                   int W, int Dd, int start, int N,
+                                                   const DistMap dm = DistMap{0, 0, 1.f, 1.f}) {
   PointGeo g;
   g.W = W; g.Hh = Hh; g.Dd = Dd;
   const float w_im = fmaf(x, (float)W, -0.5f);
@@ -195,6 +248,14 @@ __device__ __forceinline__ PointGeo point_geometry(float x, float y, float z, bo
   g.pix[1] = (g.ok2 && yl && xh && (unsigned)p1 < n) ? p1 : -1;
   g.pix[2] = (g.ok2 && yh && xh && (unsigned)p2 < n) ? p2 : -1;
   g.pix[3] = (g.ok2 && yh && xl && (unsigned)p3 < n) ? p3 : -1;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) g.dpix[k] = g.pix[k];
+  if (has_z && dm.h > 0) {
+    if (g.pix[0] >= 0) g.dpix[0] = map_row(y0, x0, dm.sy, dm.sx, dm.h, dm.w);
+    if (g.pix[1] >= 0) g.dpix[1] = map_row(y0, x1, dm.sy, dm.sx, dm.h, dm.w);
+    if (g.pix[2] >= 0) g.dpix[2] = map_row(y1, x1, dm.sy, dm.sx, dm.h, dm.w);
+    if (g.pix[3] >= 0) g.dpix[3] = map_row(y1, x0, dm.sy, dm.sx, dm.h, dm.w);
+  }
   return g;
 }
 

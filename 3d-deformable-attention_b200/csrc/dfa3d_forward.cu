@@ -37,18 +37,18 @@ __device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, 
   float x, y, z, aw;
   read_point<MODE>(a, lv, c, j, l, sm, x, y, z, aw);
   const PointGeo g = point_geometry(x, y, z, mode_has_depth(MODE), lv.h[l], lv.w[l], lv.d[l], lv.start[l],
-                                    a.N);
+                                    a.N, dist_map_of(a, lv, l));
   if (!g.ok2) return;
   float bw[4];
   bilinear_weights(g, bw);
   if (mode_has_depth(MODE)) {
     const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
-                        ((long long)c.b * a.N * a.dist_pix_stride + c.h * a.dist_head_stride);
+                        ((long long)c.b * a.Nd * a.dist_pix_stride + c.h * a.dist_head_stride);
     float lo[4], hi[4];
     const int Dlim = min(g.Dd, a.D);
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, Dlim, g.ok3, lo[k], hi[k]);
+      load_depth_pair(dist_bh, a.dist_pix_stride, g.dpix[k], g.z0, Dlim, g.ok3, lo[k], hi[k]);
     const float hd = 1.f - g.ld;
 #pragma unroll
     for (int k = 0; k < 4; ++k) ds[k] = g.ok3 ? lo[k] * hd + hi[k] * g.ld : 0.f;
@@ -75,27 +75,19 @@ __device__ __forceinline__ void fwd_point(const KArgs &a, const LevelTable &lv, 
 // ------------------------------------------------------------------------------------------------
 // fused / given-depth-score / caller-fused forward; C/V a power of two, V = channels per 16 bytes
 // ------------------------------------------------------------------------------------------------
-// 5 CTAs (40 warps) per SM: measured best; at 6+ the register cap starts to cost more than the
-// extra warps hide.
+// One item: the L*P points of (camera c.b, query, head c.h), 32 at a time; `table` is the warp's slice
+// of the row table in shared memory.
 template <typename VT, typename DT, int C, int MODE, bool WRITE_DS, bool FULL>
-__global__ void __launch_bounds__(kThreads, 5)
-dfa3d_forward_kernel(const KArgs a) {
+__device__ __forceinline__ void forward_item(const KArgs &a, const LevelTable &lv, const ItemCtx &c,
+                                             RowEntry *table, int lane) {
   constexpr int V = RowVec<VT>::kElems;   // channels per lane
   constexpr int G = C / V;                // lanes per row
   constexpr int R = 32 / G;               // rows per warp-wide request
   constexpr int U = 4;                    // requests in flight per lane
   static_assert(G >= 1 && G <= 32 && (G & (G - 1)) == 0, "C/V must be a power of two <= 32");
-
-  __shared__ LevelTable lv;
-  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
-  stage_levels(lv, a);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  ItemCtx c;
-  if (!item_context(a, warp, c)) return;
   const VT *vbase = reinterpret_cast<const VT *>(a.value) + (((long long)c.b * a.N * a.H + c.h) * C +
                                                              (lane % G) * V);
-  const RowEntry *my = rows[warp] + lane / G;
+  const RowEntry *my = table + lane / G;
 
   float acc[V];
 #pragma unroll
@@ -107,7 +99,7 @@ dfa3d_forward_kernel(const KArgs a) {
     float ds[4], wgt[4];
     int off[4];
     fwd_point<DT, MODE>(a, lv, c, chunk + lane, sm, ds, wgt, off);
-    store_rows(rows[warp], lane, off, wgt);
+    store_rows(table, lane, off, wgt);
     if (WRITE_DS && chunk + lane < a.LP)
       reinterpret_cast<float4 *>(a.ds_out)[c.pt0 + chunk + lane] = make_float4(ds[0], ds[1], ds[2], ds[3]);
     __syncwarp();
@@ -156,6 +148,24 @@ dfa3d_forward_kernel(const KArgs a) {
   }
 }
 
+// 5 CTAs (40 warps) per SM: measured best; at 6+ the register cap starts to cost more than the
+// extra warps hide.  A CTA walks DFA3D_FWD_ITEMS_PER_WARP consecutive groups of 8 items (the grid's
+// ~60 000 CTAs per camera otherwise live ~2 us each and their turnover shows: measured -7 % at 8).
+template <typename VT, typename DT, int C, int MODE, bool WRITE_DS, bool FULL>
+__global__ void __launch_bounds__(kThreads, DFA3D_FWD_MIN_CTAS)
+dfa3d_forward_kernel(const KArgs a) {
+  __shared__ LevelTable lv;
+  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
+  stage_levels(lv, a);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll 1
+  for (int it = 0; it < DFA3D_FWD_ITEMS_PER_WARP; ++it) {
+    ItemCtx c;
+    if (!item_context(a, warp, blockIdx.x * DFA3D_FWD_ITEMS_PER_WARP + it, c)) return;
+    forward_item<VT, DT, C, MODE, WRITE_DS, FULL>(a, lv, c, rows[warp], lane);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // any C: lanes stride over channels, rows walked one by one (correctness path for unusual widths)
 // ------------------------------------------------------------------------------------------------
@@ -167,7 +177,7 @@ dfa3d_forward_generic_kernel(const KArgs a) {
   stage_levels(lv, a);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   ItemCtx c;
-  if (!item_context(a, warp, c)) return;
+  if (!item_context(a, warp, blockIdx.x, c)) return;
   const int C = a.C;
   const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)c.b * a.N * a.H + c.h) * C;
   RowEntry *my = rows[warp];
@@ -215,16 +225,16 @@ dfa3d_depth_score_forward_kernel(const KArgs a) {
     const int b = (int)(item / a.items_per_cam);
     const float *lp = a.loc + pt * 3;
     const PointGeo g = point_geometry(__ldg(lp), __ldg(lp + 1), __ldg(lp + 2), true, lv.h[l], lv.w[l],
-                                      lv.d[l], lv.start[l], a.N);
+                                      lv.d[l], lv.start[l], a.N, dist_map_of(a, lv, l));
     const DT *dist_bh = reinterpret_cast<const DT *>(a.dist) +
-                        ((long long)b * a.N * a.dist_pix_stride + h * a.dist_head_stride);
+                        ((long long)b * a.Nd * a.dist_pix_stride + h * a.dist_head_stride);
     float ds[4];
     const float hd = 1.f - g.ld;
     const int Dlim = min(g.Dd, a.D);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float lo, hi;
-      load_depth_pair(dist_bh, a.dist_pix_stride, g.pix[k], g.z0, Dlim, g.ok3, lo, hi);
+      load_depth_pair(dist_bh, a.dist_pix_stride, g.dpix[k], g.z0, Dlim, g.ok3, lo, hi);
       ds[k] = g.ok3 ? lo * hd + hi * g.ld : 0.f;
     }
     reinterpret_cast<float4 *>(a.ds_out)[pt] = make_float4(ds[0], ds[1], ds[2], ds[3]);
@@ -234,8 +244,9 @@ dfa3d_depth_score_forward_kernel(const KArgs a) {
 // ------------------------------------------------------------------------------------------------
 // host-side dispatch
 // ------------------------------------------------------------------------------------------------
-static dim3 item_grid(const KArgs &a, int cams) {
-  return dim3((unsigned)((a.items_per_cam + kWarpsPerCta - 1) / kWarpsPerCta), (unsigned)cams, 1);
+static dim3 item_grid(const KArgs &a, int cams, int items_per_warp) {
+  const int per_cta = kWarpsPerCta * items_per_warp;
+  return dim3((unsigned)((a.items_per_cam + per_cta - 1) / per_cta), (unsigned)cams, 1);
 }
 
 template <typename VT, typename DT, int MODE, bool WRITE_DS, bool FULL>
@@ -246,7 +257,9 @@ static void launch_forward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
     case 4:  dfa3d_forward_kernel<VT, DT, 4 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 8:  dfa3d_forward_kernel<VT, DT, 8 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 16: dfa3d_forward_kernel<VT, DT, 16 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
-    default: dfa3d_forward_generic_kernel<VT, DT, MODE, WRITE_DS><<<grid, kThreads, 0, s>>>(a); break;
+    default:
+      dfa3d_forward_generic_kernel<VT, DT, MODE, WRITE_DS><<<item_grid(a, (int)grid.y, 1), kThreads, 0, s>>>(a);
+      break;
   }
 }
 
@@ -256,7 +269,7 @@ static cudaError_t launch_forward_vd(const KArgs &a0, cudaStream_t s) {
   for (int b0 = 0; b0 < a0.B; b0 += 65535) {      // grid.y limit
     KArgs a = a0;
     a.b0 = b0;
-    const dim3 grid = item_grid(a, min(65535, a0.B - b0));
+    const dim3 grid = item_grid(a, min(65535, a0.B - b0), DFA3D_FWD_ITEMS_PER_WARP);
     if (a.ds_out) {
       if (full) launch_forward_g<VT, DT, MODE, true, true>(a, grid, s);
       else launch_forward_g<VT, DT, MODE, true, false>(a, grid, s);

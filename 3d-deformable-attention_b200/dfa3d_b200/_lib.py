@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("DFA3D_B200_LIB") or os.path.join(_HERE, "libdfa3d_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 DTYPE_F32 = 0
 DTYPE_BF16 = 1
 MAX_LEVELS = 32
@@ -22,7 +22,12 @@ class Problem(ctypes.Structure):
     """struct dfa3d_problem."""
     _fields_ = [(n, ctypes.c_int32) for n in
                 ("B", "N", "H", "C", "D", "L", "Q", "P", "value_dtype", "dist_dtype")] + \
-               [("dist_head_stride", ctypes.c_int64)]
+               [("dist_head_stride", ctypes.c_int64), ("dist_map_h", ctypes.c_int32),
+                ("dist_map_w", ctypes.c_int32)]
+
+    def __init__(self, *args, **kw):
+        # the two dist-map fields default to 0 (dist laid out like value)
+        super().__init__(*args, **kw)
 
 
 _P = ctypes.POINTER(Problem)
@@ -38,11 +43,24 @@ ENTRY_POINTS = {
     "dfa3d_fused_backward": 12,
     "dfa3d_msda_forward": 7,
     "dfa3d_msda_backward": 10,
+    # ragged variants: the query-offset table is one more pointer, right after the descriptor
+    "dfa3d_fused_forward_ragged": 10,
+    "dfa3d_fused_backward_ragged": 13,
 }
 # entry points that take `int32_t num_anchors` right after the descriptor
 ENTRY_POINTS_WITH_ANCHORS = {
     "dfa3d_attn3d_forward": 10,
     "dfa3d_attn3d_backward": 15,
+    "dfa3d_attn3d_forward_ragged": 11,
+    "dfa3d_attn3d_backward_ragged": 16,
+}
+_I32, _I64 = ctypes.c_int32, ctypes.c_int64
+# entry points without a problem descriptor: explicit argument types
+PLAIN_ENTRY_POINTS = {
+    "dfa3d_rebatch_plan": [ctypes.c_void_p, _I32, _I32, _I32, _I32] + [ctypes.c_void_p] * 8,
+    "dfa3d_rebatch_gather": [ctypes.c_void_p] * 4 + [_I32] * 4 + [_I64, _I64] + [ctypes.c_void_p] * 2
+                            + [_I64, ctypes.c_void_p],
+    "dfa3d_rebatch_combine": [ctypes.c_void_p] * 3 + [_I32] * 4 + [ctypes.c_void_p] * 3,
 }
 
 _lib = None
@@ -70,11 +88,24 @@ def load():
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [_P, ctypes.c_int32] + [_V] * nptr
+    for name, argtypes in PLAIN_ENTRY_POINTS.items():
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = argtypes
     got = lib.dfa3d_abi_version()
     if got != ABI_VERSION:
         raise ImportError(f"libdfa3d_b200.so has ABI version {got}, this package expects {ABI_VERSION}")
     _lib = lib
     return lib
+
+
+def call_plain(name, *args):
+    """Invoke an entry point that takes no problem descriptor."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        msg = lib.dfa3d_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{name} failed ({ERROR_NAMES.get(rc, rc)}): {msg}")
 
 
 def call(name, problem, *ptrs):

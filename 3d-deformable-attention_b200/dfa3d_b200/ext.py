@@ -70,6 +70,15 @@ def _dist_problem(dist, H):
     raise RuntimeError("dist must be (B,N,H,D) or (B,N,D)")
 
 
+def _level_table(shapes, lsi, L, width):
+    """spatial_shapes must be (L, width) and level_start_index must hold L entries: the kernels read
+    entry l of both for every level l < L."""
+    if tuple(shapes.shape) != (L, width) or lsi.numel() != L:
+        raise RuntimeError(f"inconsistent shapes: spatial_shapes must be ({L},{width}) and "
+                           f"level_start_index must have {L} entries, got {tuple(shapes.shape)} and "
+                           f"{lsi.numel()}")
+
+
 def _loc_dims(loc, last):
     if loc.dim() != 6 or loc.shape[-1] != last:
         raise RuntimeError(f"sampling_locations must be (B,Q,H,L,P,{last}), got {tuple(loc.shape)}")
@@ -89,6 +98,7 @@ def ms_depth_score_sample_forward(value, value_spatial_shapes, value_level_start
     Bd, N, D, hs = _dist_problem(dist, H)
     if Bd != B or tuple(value_spatial_shapes.shape) != (L, 3):
         raise RuntimeError("inconsistent shapes between value, spatial_shapes (L,3) and sampling_loc")
+    _level_table(value_spatial_shapes, value_level_start_index, L, 3)
     _step_check(B, im2col_step)
     out = torch.empty((B, Q, H, L, P, 4), dtype=torch.float32, device=dist.device)
     pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs)
@@ -115,6 +125,9 @@ def ms_depth_score_sample_backward(value, value_spatial_shapes, value_level_star
     if grad_value.shape != dist.shape or grad_sampling_loc.shape != sampling_locations.shape \
             or tuple(grad_output.shape) != (B, Q, H, L, P, 4):
         raise RuntimeError("gradient tensors do not match their forward tensors")
+    if Bd != B:
+        raise RuntimeError("inconsistent shapes between value and sampling_loc")
+    _level_table(value_spatial_shapes, value_level_start_index, L, 3)
     _step_check(B, im2col_step)
     pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs)
     with torch.cuda.device(dist.device):
@@ -139,6 +152,7 @@ def wms_deform_attn_forward(value, value_spatial_shapes, value_level_start_index
             or tuple(depth_scores.shape) != (B, Q, H, L, P, 4):
         raise RuntimeError("inconsistent shapes between value, spatial_shapes (L,2), sampling_loc, "
                            "attn_weight and depth_score")
+    _level_table(value_spatial_shapes, value_level_start_index, L, 2)
     _step_check(B, im2col_step)
     out = torch.empty((B, Q, H * C), dtype=torch.float32, device=value.device)
     pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
@@ -170,6 +184,7 @@ def wms_deform_attn_backward(value, value_spatial_shapes, value_level_start_inde
             or grad_attn_weight.shape != attention_weights.shape \
             or grad_depth_score.shape != depth_scores.shape:
         raise RuntimeError("inconsistent shapes in wms_deform_attn_backward")
+    _level_table(value_spatial_shapes, value_level_start_index, L, 2)
     _step_check(B, im2col_step)
     pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
     with torch.cuda.device(value.device):
@@ -198,6 +213,7 @@ def ms_deform_attn_forward(value, value_spatial_shapes, value_level_start_index,
             or tuple(attention_weights.shape) != (B, Q, H, L, P):
         raise RuntimeError("inconsistent shapes between value, spatial_shapes (L,2), sampling_loc and "
                            "attn_weight")
+    _level_table(value_spatial_shapes, value_level_start_index, L, 2)
     _step_check(B, im2col_step)
     out = torch.empty((B, Q, H * C), dtype=torch.float32, device=value.device)
     pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
@@ -226,6 +242,7 @@ def ms_deform_attn_backward(value, value_spatial_shapes, value_level_start_index
             or grad_sampling_loc.shape != sampling_locations.shape \
             or grad_attn_weight.shape != attention_weights.shape:
         raise RuntimeError("inconsistent shapes in ms_deform_attn_backward")
+    _level_table(value_spatial_shapes, value_level_start_index, L, 2)
     _step_check(B, im2col_step)
     pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
     with torch.cuda.device(value.device):
@@ -251,6 +268,7 @@ def _fused_problem(value, dist, shapes3, lsi, loc3, attn):
             or tuple(attn.shape) != (B, Q, H, L, P):
         raise RuntimeError("inconsistent shapes between value, value_dpt_dist, spatial_shapes (L,3), "
                            "sampling_loc and attn_weight")
+    _level_table(shapes3, lsi, L, 3)
     return _lib.Problem(B, N, H, C, D, L, Q, P, _dt(value), _dt(dist), hs), (B, Q, H, L, P, C)
 
 
@@ -333,6 +351,7 @@ def _attn3d_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits):
             or off_d.numel() != B * Q * H * L * P or logits.numel() != B * Q * H * L * P:
         raise RuntimeError("inconsistent shapes between value, value_dpt_dist, spatial_shapes (L,3), "
                            "offsets and logits")
+    _level_table(shapes3, lsi, L, 3)
     return _lib.Problem(B, N, H, C, D, L, Q, P, _dt(value), _dt(dist), hs), Z, (B, Q, H, C)
 
 
@@ -349,6 +368,9 @@ def dfa3d_attn3d_forward(value, value_dpt_dist, value_spatial_shapes, value_leve
         out = torch.empty((B, Q, H * C), dtype=torch.float32, device=value.device)
     else:
         _chk(out, "out", _F32)
+        _same_device(value, out)
+        if out.numel() != B * Q * H * C:
+            raise RuntimeError("out has the wrong number of elements")
     with torch.cuda.device(value.device):
         _lib.call("dfa3d_attn3d_forward", pr, Z, _ptr(value), _ptr(value_dpt_dist),
                   _ptr(value_spatial_shapes), _ptr(value_level_start_index), _ptr(reference_points),
@@ -370,6 +392,8 @@ def dfa3d_attn3d_backward(value, value_dpt_dist, value_spatial_shapes, value_lev
                  (grad_value_dpt_dist, "grad_value_dpt_dist"), (grad_offsets_uv, "grad_offsets_uv"),
                  (grad_offsets_depth, "grad_offsets_depth"), (grad_logits, "grad_logits")):
         _chk(t, n, _F32)
+    _same_device(value, grad_output, grad_value, grad_value_dpt_dist, grad_offsets_uv, grad_offsets_depth,
+                 grad_logits)
     if grad_output.numel() != B * Q * H * C or grad_value.shape != value.shape \
             or grad_value_dpt_dist.shape != value_dpt_dist.shape \
             or grad_offsets_uv.shape != sampling_offsets_uv.shape \
@@ -382,3 +406,151 @@ def dfa3d_attn3d_backward(value, value_dpt_dist, value_spatial_shapes, value_lev
                   _ptr(sampling_offsets_uv), _ptr(sampling_offsets_depth), _ptr(attention_logits),
                   _ptr(grad_output), _ptr(grad_value), _ptr(grad_value_dpt_dist), _ptr(grad_offsets_uv),
                   _ptr(grad_offsets_depth), _ptr(grad_logits), _stream(value))
+
+
+# ------------------------------------------------------------------------------------------------
+# ragged variants: cameras with different numbers of queries share one launch.  Per-query tensors are
+# packed rows without a batch dimension; query_offsets (B+1 int32, CUDA) says which rows belong to
+# which camera; max_queries bounds the queries of any one camera (it sizes the launch).
+# ------------------------------------------------------------------------------------------------
+_I32 = (torch.int32,)
+
+
+def _ragged_common(value, dist, shapes3, lsi, query_offsets, max_queries, rows, per_row, names):
+    """Checks shared by the ragged entry points.  `per_row`: tensors whose first dimension is the packed
+    row count `rows`.  Returns the problem descriptor with Q = max_queries."""
+    _chk(value, "value", _VAL); _chk(dist, "value_dpt_dist", _VAL)
+    _chk(shapes3, "spatial_shapes", _I64); _chk(lsi, "level_start_index", _I64)
+    _chk(query_offsets, "query_offsets", _I32)
+    for t, n in zip(per_row, names):
+        _chk(t, n, _F32)
+        if t.shape[0] != rows:
+            raise RuntimeError(f"{n} must have {rows} packed rows, got {t.shape[0]}")
+    _same_device(value, dist, shapes3, lsi, query_offsets, *per_row)
+    B, N, H, C = value.shape
+    Bd, Nd, D, hs = _dist_problem(dist, H)
+    if (Bd, Nd) != (B, N) or query_offsets.numel() != B + 1:
+        raise RuntimeError("inconsistent shapes between value, value_dpt_dist and query_offsets (B+1)")
+    if int(max_queries) < 0:
+        raise RuntimeError("max_queries must be >= 0")
+    return B, N, H, C, D, hs
+
+
+def dfa3d_fused_forward_ragged(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                               sampling_locations, attention_weights, query_offsets, max_queries,
+                               need_depth_score=True):
+    """sampling_locations (R,H,L,P,3), attention_weights (R,H,L,P) -> (output (R,H*C), depth_score
+    (R,H,L,P,4) or None)."""
+    if sampling_locations.dim() != 5 or sampling_locations.shape[-1] != 3:
+        raise RuntimeError("sampling_locations must be (R,H,L,P,3)")
+    R, Hq, L, P, _ = sampling_locations.shape
+    B, N, H, C, D, hs = _ragged_common(value, value_dpt_dist, value_spatial_shapes,
+                                       value_level_start_index, query_offsets, max_queries, R,
+                                       (sampling_locations, attention_weights),
+                                       ("sampling_loc", "attn_weight"))
+    if Hq != H or tuple(attention_weights.shape) != (R, H, L, P):
+        raise RuntimeError("inconsistent shapes between value, sampling_loc and attn_weight")
+    _level_table(value_spatial_shapes, value_level_start_index, L, 3)
+    dev = value.device
+    out = torch.empty((R, H * C), dtype=torch.float32, device=dev)
+    ds = torch.empty((R, H, L, P, 4), dtype=torch.float32, device=dev) if need_depth_score else None
+    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(value_dpt_dist), hs)
+    with torch.cuda.device(dev):
+        _lib.call("dfa3d_fused_forward_ragged", pr, _ptr(query_offsets), _ptr(value), _ptr(value_dpt_dist),
+                  _ptr(value_spatial_shapes), _ptr(value_level_start_index), _ptr(sampling_locations),
+                  _ptr(attention_weights), _ptr(out), _ptr(ds), _stream(value))
+    return out, ds
+
+
+def dfa3d_fused_backward_ragged(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                                sampling_locations, attention_weights, query_offsets, max_queries,
+                                grad_output, grad_value, grad_value_dpt_dist, grad_sampling_loc,
+                                grad_attn_weight):
+    """Accumulates into grad_value / grad_value_dpt_dist (float32, caller-zeroed); overwrites
+    grad_sampling_loc (R,H,L,P,3) and grad_attn_weight (R,H,L,P)."""
+    R, Hq, L, P, _ = sampling_locations.shape
+    B, N, H, C, D, hs = _ragged_common(
+        value, value_dpt_dist, value_spatial_shapes, value_level_start_index, query_offsets, max_queries,
+        R, (sampling_locations, attention_weights, grad_output, grad_sampling_loc, grad_attn_weight),
+        ("sampling_loc", "attn_weight", "grad_output", "grad_sampling_loc", "grad_attn_weight"))
+    _chk(grad_value, "grad_value", _F32); _chk(grad_value_dpt_dist, "grad_value_dpt_dist", _F32)
+    _same_device(value, grad_value, grad_value_dpt_dist)
+    if Hq != H or grad_output.numel() != R * H * C or grad_value.shape != value.shape \
+            or grad_value_dpt_dist.shape != value_dpt_dist.shape \
+            or grad_sampling_loc.shape != sampling_locations.shape \
+            or grad_attn_weight.shape != attention_weights.shape:
+        raise RuntimeError("inconsistent shapes in dfa3d_fused_backward_ragged")
+    _level_table(value_spatial_shapes, value_level_start_index, L, 3)
+    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(value_dpt_dist), hs)
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_fused_backward_ragged", pr, _ptr(query_offsets), _ptr(value),
+                  _ptr(value_dpt_dist), _ptr(value_spatial_shapes), _ptr(value_level_start_index),
+                  _ptr(sampling_locations), _ptr(attention_weights), _ptr(grad_output), _ptr(grad_value),
+                  _ptr(grad_value_dpt_dist), _ptr(grad_sampling_loc), _ptr(grad_attn_weight),
+                  _stream(value))
+
+
+def _attn3d_ragged_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits, query_offsets,
+                           max_queries, extra=(), extra_names=()):
+    if off_uv.dim() != 5 or off_uv.shape[-1] != 2:
+        raise RuntimeError(f"sampling_offsets_uv must be (R,H,L,P,2), got {tuple(off_uv.shape)}")
+    R, Hq, L, P, _ = off_uv.shape
+    B, N, H, C, D, hs = _ragged_common(
+        value, dist, shapes3, lsi, query_offsets, max_queries, R,
+        (ref, off_uv, off_d, logits) + tuple(extra),
+        ("reference_points", "sampling_offsets_uv", "sampling_offsets_depth", "attention_logits")
+        + tuple(extra_names))
+    if ref.dim() != 3 or ref.shape[-1] != 3:
+        raise RuntimeError(f"reference_points must be (R,Z,3), got {tuple(ref.shape)}")
+    Z = ref.shape[1]
+    if Z <= 0 or P % Z != 0:
+        raise RuntimeError(f"the number of anchors ({Z}) must divide the points per level ({P})")
+    if Hq != H or off_d.numel() != R * H * L * P or logits.numel() != R * H * L * P:
+        raise RuntimeError("inconsistent shapes between value, offsets and logits")
+    _level_table(shapes3, lsi, L, 3)
+    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(dist), hs)
+    return pr, Z, (R, H, C)
+
+
+def dfa3d_attn3d_forward_ragged(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                                reference_points, sampling_offsets_uv, sampling_offsets_depth,
+                                attention_logits, query_offsets, max_queries):
+    """reference_points (R,Z,3); sampling_offsets_uv (R,H,L,P,2); sampling_offsets_depth (R,H,L,P);
+    attention_logits (R,H,L*P).  Returns output (R,H*C)."""
+    pr, Z, (R, H, C) = _attn3d_ragged_problem(
+        value, value_dpt_dist, value_spatial_shapes, value_level_start_index, reference_points,
+        sampling_offsets_uv, sampling_offsets_depth, attention_logits, query_offsets, max_queries)
+    out = torch.empty((R, H * C), dtype=torch.float32, device=value.device)
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_attn3d_forward_ragged", pr, Z, _ptr(query_offsets), _ptr(value),
+                  _ptr(value_dpt_dist), _ptr(value_spatial_shapes), _ptr(value_level_start_index),
+                  _ptr(reference_points), _ptr(sampling_offsets_uv), _ptr(sampling_offsets_depth),
+                  _ptr(attention_logits), _ptr(out), _stream(value))
+    return out
+
+
+def dfa3d_attn3d_backward_ragged(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                                 reference_points, sampling_offsets_uv, sampling_offsets_depth,
+                                 attention_logits, query_offsets, max_queries, grad_output, grad_value,
+                                 grad_value_dpt_dist, grad_offsets_uv, grad_offsets_depth, grad_logits):
+    """Accumulates into grad_value / grad_value_dpt_dist (float32, caller-zeroed); overwrites the
+    gradients of the offsets and of the logits (packed rows)."""
+    pr, Z, (R, H, C) = _attn3d_ragged_problem(
+        value, value_dpt_dist, value_spatial_shapes, value_level_start_index, reference_points,
+        sampling_offsets_uv, sampling_offsets_depth, attention_logits, query_offsets, max_queries,
+        (grad_output, grad_offsets_uv, grad_offsets_depth, grad_logits),
+        ("grad_output", "grad_offsets_uv", "grad_offsets_depth", "grad_logits"))
+    _chk(grad_value, "grad_value", _F32); _chk(grad_value_dpt_dist, "grad_value_dpt_dist", _F32)
+    _same_device(value, grad_value, grad_value_dpt_dist)
+    if grad_output.numel() != R * H * C or grad_value.shape != value.shape \
+            or grad_value_dpt_dist.shape != value_dpt_dist.shape \
+            or grad_offsets_uv.shape != sampling_offsets_uv.shape \
+            or grad_offsets_depth.numel() != sampling_offsets_depth.numel() \
+            or grad_logits.numel() != attention_logits.numel():
+        raise RuntimeError("inconsistent shapes in dfa3d_attn3d_backward_ragged")
+    with torch.cuda.device(value.device):
+        _lib.call("dfa3d_attn3d_backward_ragged", pr, Z, _ptr(query_offsets), _ptr(value),
+                  _ptr(value_dpt_dist), _ptr(value_spatial_shapes), _ptr(value_level_start_index),
+                  _ptr(reference_points), _ptr(sampling_offsets_uv), _ptr(sampling_offsets_depth),
+                  _ptr(attention_logits), _ptr(grad_output), _ptr(grad_value), _ptr(grad_value_dpt_dist),
+                  _ptr(grad_offsets_uv), _ptr(grad_offsets_depth), _ptr(grad_logits), _stream(value))

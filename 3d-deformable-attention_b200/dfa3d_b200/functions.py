@@ -178,6 +178,77 @@ class DeformableAttn3DFromOffsetsFunction(Function):
         return grad_value, grad_dist, None, None, None, grad_uv, grad_d, grad_logits
 
 
+class MultiScale3DDeformableAttnRaggedFunction(Function):
+    """The one-stage operator for cameras with different numbers of queries: sampling_locations
+    (R,H,L,P,3) and attention_weights (R,H,L,P) are packed rows, camera b owning rows
+    [query_offsets[b], query_offsets[b+1]); max_queries bounds the rows of one camera.  Returns
+    (output (R,H*C), depth_score (R,H,L,P,4) or None).  The reference pads every camera to the longest
+    list instead (spatial_cross_attention.py:707-722) and calls the dense Function."""
+
+    @staticmethod
+    def forward(ctx, value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                sampling_locations, attention_weights, query_offsets, max_queries,
+                return_depth_score=True):
+        ctx.max_queries = int(max_queries)
+        ctx.set_materialize_grads(False)
+        output, depth_score = ext_module.dfa3d_fused_forward_ragged(
+            value, value_dpt_dist, value_spatial_shapes, value_level_start_index, sampling_locations,
+            attention_weights, query_offsets, ctx.max_queries, need_depth_score=return_depth_score)
+        ctx.save_for_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                              sampling_locations, attention_weights, query_offsets)
+        return output, depth_score
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output, grad_depth_score_=None):
+        if grad_depth_score_ is not None and grad_depth_score_.sum() != 0.0:
+            raise NotImplementedError      # as the dense Function: depth_score carries no gradient
+        value, dist, shapes, lsi, loc, attn, q_off = ctx.saved_tensors
+        if grad_output is None:
+            return (None,) * 9
+        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_dist = torch.zeros(dist.shape, dtype=torch.float32, device=dist.device)
+        grad_sampling_loc = torch.empty_like(loc)
+        grad_attn_weight = torch.empty_like(attn)
+        ext_module.dfa3d_fused_backward_ragged(
+            value, dist, shapes, lsi, loc, attn, q_off, ctx.max_queries, grad_output.contiguous(),
+            grad_value, grad_dist, grad_sampling_loc, grad_attn_weight)
+        return grad_value, grad_dist, None, None, grad_sampling_loc, grad_attn_weight, None, None, None
+
+
+class DeformableAttn3DFromOffsetsRaggedFunction(Function):
+    """DeformableAttn3DFromOffsetsFunction on packed rows: reference_points (R,Z,3),
+    sampling_offsets_uv (R,H,L,P,2), sampling_offsets_depth (R,H,L,P), attention_logits (R,H,L*P);
+    camera b owns rows [query_offsets[b], query_offsets[b+1]).  Returns output (R,H*C)."""
+
+    @staticmethod
+    def forward(ctx, value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                reference_points, sampling_offsets_uv, sampling_offsets_depth, attention_logits,
+                query_offsets, max_queries):
+        ctx.max_queries = int(max_queries)
+        output = ext_module.dfa3d_attn3d_forward_ragged(
+            value, value_dpt_dist, value_spatial_shapes, value_level_start_index, reference_points,
+            sampling_offsets_uv, sampling_offsets_depth, attention_logits, query_offsets, ctx.max_queries)
+        ctx.save_for_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
+                              reference_points, sampling_offsets_uv, sampling_offsets_depth,
+                              attention_logits, query_offsets)
+        return output
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        value, dist, shapes, lsi, ref, off_uv, off_d, logits, q_off = ctx.saved_tensors
+        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_dist = torch.zeros(dist.shape, dtype=torch.float32, device=dist.device)
+        grad_uv = torch.empty_like(off_uv)
+        grad_d = torch.empty_like(off_d)
+        grad_logits = torch.empty_like(logits)
+        ext_module.dfa3d_attn3d_backward_ragged(value, dist, shapes, lsi, ref, off_uv, off_d, logits, q_off,
+                                                ctx.max_queries, grad_output.contiguous(), grad_value,
+                                                grad_dist, grad_uv, grad_d, grad_logits)
+        return grad_value, grad_dist, None, None, None, grad_uv, grad_d, grad_logits, None, None
+
+
 def _fp32_variant(cls, name):
     """Same Function with inputs cast to float32 when autocast is active."""
     fwd = torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float32)(cls.forward)
@@ -195,3 +266,7 @@ MultiScaleDeformableAttnFunction_fp32 = _fp32_variant(
     MultiScaleDeformableAttnFunction, "MultiScaleDeformableAttnFunction_fp32")
 DeformableAttn3DFromOffsetsFunction_fp32 = _fp32_variant(
     DeformableAttn3DFromOffsetsFunction, "DeformableAttn3DFromOffsetsFunction_fp32")
+MultiScale3DDeformableAttnRaggedFunction_fp32 = _fp32_variant(
+    MultiScale3DDeformableAttnRaggedFunction, "MultiScale3DDeformableAttnRaggedFunction_fp32")
+DeformableAttn3DFromOffsetsRaggedFunction_fp32 = _fp32_variant(
+    DeformableAttn3DFromOffsetsRaggedFunction, "DeformableAttn3DFromOffsetsRaggedFunction_fp32")

@@ -7,17 +7,58 @@
     BEVFormer encoder layer (…/modules/encoder.py:249-413 with the 'cross_attn', 'norm', 'ffn',
     'norm' operation order), used for the training-step configuration.
 
+  * ``point_sampling`` -- the projection of the pillar reference points into the cameras that yields
+    ``reference_points_cam`` and ``bev_mask`` (…/modules/encoder.py:421-476).
+
 Parameter names, shapes and initialisation follow the reference so that its checkpoints load; the
 registry / config plumbing of mmcv is not reproduced.  Differences in how the operator is fed:
 the depth distribution is passed as (B, N, D) shared by all heads instead of being repeated per head
-(:497 in the reference), and the per-camera re-batching uses index tensors instead of Python loops.
+(:497 in the reference); the per-camera re-batching keeps exactly the (camera, query) pairs that are
+visible, as packed rows moved by kernels (``rebatch.RebatchPlan``), instead of Python loops over tensors
+padded to the longest camera, and the operator is called once for all cameras with their row offsets.
 """
 import math
 
 import torch
 import torch.nn as nn
 
-from .functions import DeformableAttn3DFromOffsetsFunction_fp32, MultiScale3DDeformableAttnFunction_fp32
+from .functions import (DeformableAttn3DFromOffsetsFunction_fp32,
+                        DeformableAttn3DFromOffsetsRaggedFunction_fp32,
+                        MultiScale3DDeformableAttnFunction_fp32,
+                        MultiScale3DDeformableAttnRaggedFunction_fp32)
+from .rebatch import (CombineCamerasFunction, GatherQueriesFunction, GatherSharedRowsFunction, RebatchPlan,
+                      gather_per_camera)
+
+
+def point_sampling(reference_points, pc_range, lidar2img, img_shape, d_bound):
+    """Project the pillar reference points into every camera (encoder.py:421-476).
+
+    reference_points (bs, Z, Q, 3) in [0,1]^3 of the BEV volume; pc_range = (x0, y0, z0, x1, y1, z1);
+    lidar2img (bs, cams, 4, 4); img_shape = (height, width) of the padded images; d_bound = (near, far,
+    step) of the depth bins.  Returns reference_points_cam (cams, bs, Q, Z, 3) = (x / width, y / height,
+    (depth - near) / (far - near)) and bev_mask (cams, bs, Q, Z): in front of the camera and inside the
+    image."""
+    ref = reference_points.clone().float()
+    ref[..., 0:1] = ref[..., 0:1] * (pc_range[3] - pc_range[0]) + pc_range[0]
+    ref[..., 1:2] = ref[..., 1:2] * (pc_range[4] - pc_range[1]) + pc_range[1]
+    ref[..., 2:3] = ref[..., 2:3] * (pc_range[5] - pc_range[2]) + pc_range[2]
+    ref = torch.cat((ref, torch.ones_like(ref[..., :1])), -1).permute(1, 0, 2, 3)      # (Z, bs, Q, 4)
+    Z, bs, Q = ref.shape[:3]
+    cams = lidar2img.size(1)
+    ref = ref.view(Z, bs, 1, Q, 4, 1)
+    mat = lidar2img.float().view(1, bs, cams, 1, 4, 4)
+    cam = torch.matmul(mat, ref).squeeze(-1)                                           # (Z, bs, cams, Q, 4)
+    eps = 1e-5
+    mask = cam[..., 2:3] > eps
+    xy = cam[..., 0:2] / torch.maximum(cam[..., 2:3], torch.ones_like(cam[..., 2:3]) * eps)
+    x = xy[..., 0] / img_shape[1]
+    y = xy[..., 1] / img_shape[0]
+    z = (cam[..., 2] - d_bound[0]) / (d_bound[1] - d_bound[0])
+    out = torch.stack((x, y, z), -1)
+    mask = (mask & (out[..., 1:2] > 0.0) & (out[..., 1:2] < 1.0) & (out[..., 0:1] < 1.0)
+            & (out[..., 0:1] > 0.0))
+    mask = torch.nan_to_num(mask)
+    return out.permute(2, 1, 3, 0, 4).contiguous(), mask.permute(2, 1, 3, 0, 4).squeeze(-1).contiguous()
 
 
 def assemble_sampling_locations(reference_points, offsets_uv, offsets_depth, spatial_shapes, depth_bins):
@@ -84,16 +125,22 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
             nn.init.zeros_(self.value_proj.bias)
 
     def forward(self, query, value, value_dpt_dist, reference_points, spatial_shapes, level_start_index,
-                query_pos=None, key_padding_mask=None):
+                query_pos=None, key_padding_mask=None, query_offsets=None, max_queries=None):
         """query (bs, Q, E); value (bs, N, E); value_dpt_dist (bs, N, D); reference_points
         (bs, Q, Z, 3); spatial_shapes (L, 2) int64; level_start_index (L) int64.
-        Returns (output (bs, Q, E), weight_update (bs, Q, H, 1))  -- :428-583."""
+        Returns (output (bs, Q, E), weight_update (bs, Q, H, 1))  -- :428-583.
+
+        Packed rows (cameras with different numbers of queries): pass ``query_offsets`` (bs+1 int32,
+        CUDA; element b of value owns the rows [query_offsets[b], query_offsets[b+1])) and
+        ``max_queries``; then query is (R, E), reference_points (R, Z, 3), and the results are
+        (R, E) and (R, H, 1).  value / value_dpt_dist are batch-first in this mode."""
+        ragged = query_offsets is not None
         if query_pos is not None:
             query = query + query_pos
-        if not self.batch_first:
+        if not self.batch_first and not ragged:
             query, value = query.permute(1, 0, 2), value.permute(1, 0, 2)
-        bs, Q, _ = query.shape
-        _, N, _ = value.shape
+        lead = query.shape[:-1]                              # (bs, Q) or (R,)
+        bs, N, _ = value.shape
         H, L, P = self.num_heads, self.num_levels, self.num_points
         D = value_dpt_dist.shape[-1]
         value = self.value_proj(value)
@@ -104,28 +151,36 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
             raise ValueError("Last dim of reference_points must be 3 (x, y, depth), but got "
                              f"{reference_points.shape[-1]} instead.")
         shapes3 = torch.cat([spatial_shapes, torch.full_like(spatial_shapes[:, :1], D)], -1).contiguous()
-        off_uv = self.sampling_offsets(query).view(bs, Q, H, L, P, 2)
-        off_d = self.sampling_offsets_depth(query).view(bs, Q, H, L, P, 1)
-        logits = self.attention_weights(query).view(bs, Q, H, L * P)
+        off_uv = self.sampling_offsets(query).view(*lead, H, L, P, 2)
+        off_d = self.sampling_offsets_depth(query).view(*lead, H, L, P, 1)
+        logits = self.attention_weights(query).view(*lead, H, L * P)
         if self.fuse_input_ops and not self.compute_weight_update:
+            if ragged:
+                output = DeformableAttn3DFromOffsetsRaggedFunction_fp32.apply(
+                    value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
+                    reference_points.contiguous(), off_uv, off_d, logits, query_offsets, max_queries)
+                return output, None
             output = DeformableAttn3DFromOffsetsFunction_fp32.apply(
                 value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
                 reference_points.contiguous(), off_uv, off_d, logits)
             return (output if self.batch_first else output.permute(1, 0, 2)), None
-        attn = logits.softmax(-1).view(bs, Q, H, L, P)
-        loc = assemble_sampling_locations(reference_points, off_uv, off_d, spatial_shapes, D)
-        if self.compute_weight_update:
+        attn = logits.softmax(-1).view(*lead, H, L, P)
+        if ragged:
+            loc = assemble_sampling_locations(reference_points[None], off_uv[None], off_d[None],
+                                              spatial_shapes, D)[0]
+            output, depth_score = MultiScale3DDeformableAttnRaggedFunction_fp32.apply(
+                value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
+                loc.contiguous(), attn.contiguous(), query_offsets, max_queries, self.compute_weight_update)
+        else:
+            loc = assemble_sampling_locations(reference_points, off_uv, off_d, spatial_shapes, D)
             output, depth_score = MultiScale3DDeformableAttnFunction_fp32.apply(
                 value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
-                loc.contiguous(), attn.contiguous(), self.im2col_step)
+                loc.contiguous(), attn.contiguous(), self.im2col_step, self.compute_weight_update)
+        weight_update = None
+        if self.compute_weight_update:
             # mean depth score of a point's four corners, weighted by the attention (:579)
             weight_update = (depth_score.mean(-1) * attn).flatten(-2).sum(-1, keepdim=True)
-        else:
-            output, _ = MultiScale3DDeformableAttnFunction_fp32.apply(
-                value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
-                loc.contiguous(), attn.contiguous(), self.im2col_step, False)
-            weight_update = None
-        if not self.batch_first:
+        if not self.batch_first and not ragged:
             output = output.permute(1, 0, 2)
         return output, weight_update
 
@@ -148,56 +203,40 @@ class SpatialCrossAttention_DFA3D(nn.Module):
         nn.init.xavier_uniform_(self.output_proj.weight)
         nn.init.zeros_(self.output_proj.bias)
 
-    @staticmethod
-    def rebatch_indexes(bev_mask):
-        """bev_mask (num_cams, bs, Q, Z) bool -> (index (num_cams, max_len) int64 padded with 0,
-        valid (num_cams, max_len) bool).  Like the reference (:703-707) the queries of a camera are
-        those that camera sees in batch element 0."""
-        hit = bev_mask[:, 0].sum(-1) > 0                                  # (cams, Q)
-        lens = hit.sum(-1)
-        max_len = int(lens.max())
-        order = torch.argsort((~hit).to(torch.int8), dim=-1, stable=True)  # seen queries first, in order
-        index = order[:, :max_len]
-        valid = torch.arange(max_len, device=hit.device)[None] < lens[:, None]
-        return index.masked_fill(~valid, 0), valid
-
     def forward(self, query, key=None, value=None, value_dpt_dist=None, reference_points_cam=None,
                 bev_mask=None, spatial_shapes=None, level_start_index=None, residual=None,
-                query_pos=None):
+                query_pos=None, rebatch_plan=None):
         """query (bs, Q, E); value (num_cams, N, bs, E) (`key` is accepted and, as in the reference,
         not used by the attention); value_dpt_dist (num_cams, N, bs, D);
         reference_points_cam (num_cams, bs, Q, Z, 3); bev_mask (num_cams, bs, Q, Z).
-        Returns (bs, Q, E)."""
+        ``rebatch_plan``: a ``RebatchPlan`` of this bev_mask built earlier (bev_mask is geometry: one
+        plan serves every layer of a frame); without it the plan is built here, which reads the packed
+        row count back from the device once.  Returns (bs, Q, E)."""
         inp_residual = query if residual is None else residual
         if query_pos is not None:
             query = query + query_pos
         bs, Q, E = query.shape
         cams = self.num_cams
-        Z = reference_points_cam.size(3)
-        index, valid = self.rebatch_indexes(bev_mask)                       # (cams, max_len)
-        max_len = index.shape[1]
-        vf = valid[None, :, :, None].to(query.dtype)
-        q_re = query[:, index] * vf                                         # (bs, cams, max_len, E)
-        ref = reference_points_cam.permute(1, 0, 2, 3, 4)                   # (bs, cams, Q, Z, 3)
-        ref_re = torch.gather(ref, 2, index[None, :, :, None, None].expand(bs, cams, max_len, Z, 3))
-        ref_re = ref_re * valid[None, :, :, None, None].to(ref.dtype)
+        plan = rebatch_plan if rebatch_plan is not None else RebatchPlan(bev_mask)
+        if (plan.cams, plan.bs, plan.Q) != (cams, bs, Q):
+            raise RuntimeError("rebatch_plan does not belong to this bev_mask / query")
+        q_rows = GatherQueriesFunction.apply(query.float(), plan)                 # (bs*T, E)
+        ref_rows = gather_per_camera(reference_points_cam.float(), plan)          # (bs*T, Z, 3)
         N = value.shape[1]
-        value = value.permute(2, 0, 1, 3).reshape(bs * cams, N, E)
+        value = value.permute(2, 0, 1, 3).reshape(bs * cams, N, E)                # element j*cams + i
         dist = value_dpt_dist.permute(2, 0, 1, 3).reshape(bs * cams, N, -1)
-        out, update_weight = self.deformable_attention(
-            query=q_re.reshape(bs * cams, max_len, E), value=value, value_dpt_dist=dist,
-            reference_points=ref_re.reshape(bs * cams, max_len, Z, 3), spatial_shapes=spatial_shapes,
-            level_start_index=level_start_index)
-        out = out.view(bs, cams, max_len, E)
+        out_rows, update_weight = self.deformable_attention(
+            query=q_rows, value=value, value_dpt_dist=dist, reference_points=ref_rows,
+            spatial_shapes=spatial_shapes, level_start_index=level_start_index,
+            query_offsets=plan.op_offsets, max_queries=plan.max_queries)
         if self.use_empty:
-            update_weight = update_weight.view(bs, cams, max_len, self.num_head, 1)
-            empty = self.empty_query.weight.view(self.bev_h * self.bev_w, self.num_head, E)[index]
-            out = out + ((1 - update_weight) * (empty[None] * vf[..., None])).mean(-2)
-        slots = torch.zeros_like(query)
-        slots.index_put_((torch.arange(bs, device=query.device)[:, None, None].expand(bs, cams, max_len),
-                          index[None].expand(bs, cams, max_len)), out * vf, accumulate=True)
-        count = (bev_mask.sum(-1) > 0).permute(1, 2, 0).sum(-1).clamp(min=1.0)
-        slots = self.output_proj(slots / count[..., None])
+            # :721-722, :739-740 -- rows whose depth-weighted attention found little get the learned
+            # per-(BEV cell, head) empty embedding instead
+            empty = GatherSharedRowsFunction.apply(
+                self.empty_query.weight.view(self.bev_h * self.bev_w, self.num_head * E), plan)
+            out_rows = out_rows + ((1 - update_weight) * empty.view(-1, self.num_head, E)).mean(-2)
+        slots = CombineCamerasFunction.apply(out_rows, plan)                      # sum over cameras / count
+        slots = self.output_proj(slots)
         return self.dropout(slots) + inp_residual
 
 
@@ -227,6 +266,8 @@ class SCAEncoderStack(nn.Module):
         self.layers = nn.ModuleList(SCAEncoderLayer(**layer_kw) for _ in range(num_layers))
 
     def forward(self, query, **kw):
+        if kw.get("rebatch_plan") is None:          # bev_mask is the same for every layer: one plan
+            kw = dict(kw, rebatch_plan=RebatchPlan(kw["bev_mask"]))
         for layer in self.layers:
             query = layer(query, **kw)
         return query

@@ -12,8 +12,10 @@ are independent); the job value is the points of all ranks over the slowest rank
 
 Printed by rank 0: ONE JSON line with
   value      device-resident throughput (inputs in HBM, CUDA-event timed, max over ranks)
-  e2e        the same step through the public autograd API from pinned HOST buffers, host<->device
-             copies inside the timed region
+  e2e        the same step through the host-buffer API (dfa3d_b200.HostPipeline: pinned HOST tensors
+             in, pinned host tensors out; it calls the extension-level entry points, not the autograd
+             Functions), host<->device copies inside the timed region; `copy_floor_ms` beside it is the
+             same pipeline with the kernels left out
   roofline   the dominant kernel (backward) against the measured HBM copy bandwidth
   cpu_baseline  the CPU oracle (C + OpenMP port of the reference kernels) on a bounded sample
 ``--impl reference`` times the reference's own CUDA op (unmodified sources built for sm_100a into
@@ -33,13 +35,11 @@ sys.path[:0] = [os.path.join(ROOT, "3d-deformable-attention_b200")]
 import torch  # noqa: E402
 import torch.distributed as dist_  # noqa: E402
 
-# DRAM bytes per launch from the committed ncu captures (dram__bytes_read.sum + dram__bytes_write.sum),
-# see profiles/.  Keyed by workload; None = not captured.
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of the same
+# kernels on 2 of the 6 cameras, times 3: cameras are independent and traffic grows in proportion).
+# Keyed by workload; a workload without a capture reports null.
 NCU_DRAM_TRAFFIC = {
-    # profiles/dfa3d_forward_backward_cfg2_2cameras_ncu_full.md: 2-camera capture x 3 (cameras are
-    # independent, traffic grows in proportion)
     "cfg2": {"forward": 3 * (164.163584e6 + 18.407680e6), "backward": 3 * (409.077760e6 + 212.663808e6)},
-    # profiles/dfa3d_forward_backward_cfg3_bf16_2cameras_ncu_full.md
     "cfg3": {"forward": 3 * (121.428480e6 + 14.806016e6), "backward": 3 * (242.028032e6 + 142.101504e6)},
 }
 
@@ -83,7 +83,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.01)
+            self._stop.wait(0.001)
 
     def start(self):
         if self.nv:
@@ -107,7 +107,7 @@ def measured_peak_gbs():
             return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
         except Exception:
             pass
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s)"
 
 
 def cpu_baseline(w, budget_cameras=1):
@@ -166,13 +166,29 @@ class OursRunner:
         self.ext.dfa3d_fused_backward(self.value, self.dist, t["shapes"], t["lsi"], t["loc"], t["attn"],
                                       t["grad_out"], self.gv, self.gd, self.gl, self.ga, 64)
 
-    def e2e_step(self, host, pinned_out):
+    def e2e_step(self, host, pinned_out, join=True, copies_only=False):
         """Public host-buffer API (dfa3d_b200.HostPipeline): every input is copied host->device, the
-        output and all four gradients device->host, per camera, overlapped with the kernels."""
+        output and all four gradients device->host, per camera, overlapped with the kernels.
+        join=False lets consecutive steps overlap (the caller joins after the last one)."""
         if getattr(self, "pipe", None) is None:
             from dfa3d_b200 import HostPipeline
             self.pipe = HostPipeline(self.t["shapes"], self.t["lsi"], self.t["loc"].device)
-        self.pipe.run(host, pinned_out)
+        self.pipe.run(host, pinned_out, join=join, copies_only=copies_only)
+
+    def e2e_join(self):
+        self.pipe.join()
+
+    def function_step(self):
+        """The same step through the one-stage autograd Function, the way the reference arm is driven:
+        fresh leaves, output and depth_score allocated by forward, gradients allocated (and the two
+        accumulated ones zeroed) by backward."""
+        import dfa3d_b200
+        t = self.t
+        leaves = [self.value.detach().requires_grad_(True), self.dist.detach().requires_grad_(True),
+                  t["loc"].detach().requires_grad_(True), t["attn"].detach().requires_grad_(True)]
+        out, _ = dfa3d_b200.MultiScale3DDeformableAttnFunction_fp32.apply(
+            leaves[0], leaves[1], t["shapes"], t["lsi"], leaves[2], leaves[3], 64)
+        out.backward(t["grad_out"])
 
 
 class ReferenceRunner:
@@ -199,7 +215,10 @@ class ReferenceRunner:
     def backward(self):
         self.out.backward(self.t["grad_out"])
 
-    def e2e_step(self, host, pinned_out):
+    def e2e_join(self):
+        pass
+
+    def e2e_step(self, host, pinned_out, join=True, copies_only=False):
         dev = self.t["loc"].device
         w = self.w
         value = host["value"].to(dev, non_blocking=True).requires_grad_(True)
@@ -390,8 +409,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", default="cfg2")
-    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the side measurements (cfg3, Function-level step, memory-stream floor)")
     ap.add_argument("--scaling", choices=("weak", "strong"), default="weak",
                     help="weak: 6 cameras per GPU (default, the headline); strong: one batch, queries "
                          "split over the GPUs with an all-reduce of the value/dist gradients")
@@ -505,10 +526,39 @@ def main():
     if a.e2e_steps > 0:
         e2e = measure_e2e(a, w, d, dev, world, runner, barrier)
 
+    extra = {}
+    if a.impl == "ours" and not a.no_extras:
+        # the same step through the autograd Function with its allocations: how the reference arm's
+        # device-timed figure is taken
+        for _ in range(2):
+            runner.function_step()
+        n = max(5, min(a.steps, 20))
+        extra["function_level_ms"] = _timed(lambda i: runner.function_step(), n, dev, world, barrier)
+        extra["function_level"] = ("MultiScale3DDeformableAttnFunction_fp32.apply + backward, "
+                                   "allocations and depth_score output included")
+        extra.update(measure_extras(a, w, dev, world, rank, barrier))
+        if rank == 0 and w.L * w.P == 32 and w.H == 8 and w.C == 32 and w.value_dtype == "fp32":
+            extra["memory_stream_floor"] = memory_stream_floor(w)
+
     if rank == 0:
-        report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e)
+        report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e, extra)
     if world > 1:
         dist_.destroy_process_group()
+
+
+def _timed(fn, n, dev, world, barrier):
+    """n calls of fn bracketed by barrier + synchronize, CUDA events, max over ranks -> ms per call."""
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        fn(i)
+    e1.record()
+    barrier()
+    tm = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist_.all_reduce(tm, op=dist_.ReduceOp.MAX)
+    return float(tm.item()) / n
 
 
 def measure_e2e(a, w, d, dev, world, runner, barrier):
@@ -523,26 +573,66 @@ def measure_e2e(a, w, d, dev, world, runner, barrier):
                   "grad_attn": torch.empty_like(d["attn"]).pin_memory()}
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = sum(v.numel() * v.element_size() for v in pinned_out.values())
+    n = a.e2e_steps
     for _ in range(2):
         runner.e2e_step(host, pinned_out)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(a.e2e_steps):
-        runner.e2e_step(host, pinned_out)
-    e1.record()
-    barrier()
-    em = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist_.all_reduce(em, op=dist_.ReduceOp.MAX)
-    e2e_ms = float(em.item()) / a.e2e_steps
+    # every step copies all inputs in and all results out; consecutive steps may overlap (the first
+    # copies of step i+1 travel while the last results of step i leave), the last step is joined
+    # before the clock stops
+    last = n - 1
+    e2e_ms = _timed(lambda i: runner.e2e_step(host, pinned_out, join=(i == last)), n, dev, world, barrier)
     assert torch.isfinite(pinned_out["out"]).all()
-    return {"value": w.points * world / (e2e_ms * 1e-3), "unit": "sampled points/s",
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-            "steps": a.e2e_steps}
+    res = {"value": w.points * world / (e2e_ms * 1e-3), "unit": "sampled points/s",
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n}
+    if a.impl == "ours":
+        # one step at a time (each step joined and synchronised before the next starts)
+        res["ms_per_step_one_at_a_time"] = _timed(
+            lambda i: (runner.e2e_step(host, pinned_out), torch.cuda.synchronize()), n, dev, world, barrier)
+        # the same copies in the same order with the kernels left out: what the host link allows
+        res["copy_floor_ms"] = _timed(
+            lambda i: runner.e2e_step(host, pinned_out, join=(i == last), copies_only=True), n, dev, world,
+            barrier)
+        res["copy_floor_gbs_each_way"] = h2d / (res["copy_floor_ms"] * 1e-3) / 1e9
+        res["api"] = "dfa3d_b200.HostPipeline.run (extension-level entry points; not the autograd Functions)"
+    return res
 
 
-def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e):
+def measure_extras(a, w, dev, world, rank, barrier):
+    """Driver-visible side measurements on this rank's shard, each the max over ranks:
+    cfg3 (bf16 storage of value and dist) forward-only and forward+backward, and the headline step
+    through the autograd Function with its allocations."""
+    from dfa3d_b200 import workloads as wl
+    extra = {}
+    if w.name == "cfg2":
+        w3 = wl.WORKLOADS["cfg3"].with_(B=w.B)
+        d3 = wl.make_inputs(w3, seed=w3.seed + 1000 * rank)
+        r3 = OursRunner(w3, {k: v.to(dev) for k, v in d3.items()})
+        for _ in range(3):
+            r3.forward(); r3.zero(); r3.backward()
+        n = max(10, min(a.steps, 50))
+        f_ms = _timed(lambda i: r3.forward(), n, dev, world, barrier)
+        s_ms = _timed(lambda i: (r3.forward(), r3.zero(), r3.backward()), n, dev, world, barrier)
+        extra["cfg3"] = {"workload": "cfg3: cfg2 shapes, bf16 value and dist, fp32 math and gradients",
+                         "cameras_per_gpu": w3.B, "n_gpus": world, "steps": n,
+                         "forward_only_ms": f_ms, "forward_only_points_per_s": w3.points * world / (f_ms * 1e-3),
+                         "fwd_bwd_ms": s_ms, "fwd_bwd_points_per_s": w3.points * world / (s_ms * 1e-3)}
+        del r3
+    return extra
+def memory_stream_floor(w):
+    """Lower bounds of the two kernels from the measured rates of the memory primitives they are made
+    of (dfa3d_b200.rates replays a launch's address stream without the arithmetic)."""
+    try:
+        from dfa3d_b200 import rates
+        f = rates.floors(w.levels, w.P, w.D, w.Q, w.B)
+        f["what"] = ("probe launches with this workload's address stream: forward = value-row gathers + "
+                     "dist-pair gathers; backward = the same gathers + grad_value row reductions + "
+                     "grad_dist pair reductions; reductions only = what the L2 reduction units alone need")
+        return f
+    except Exception as e:          # measurement aid only: never fail the bench over it
+        return {"unavailable": str(e)}
+
+
+def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e, extra=None):
     peak, peak_src = measured_peak_gbs()
     fwd_b, bwd_b = w.algorithmic_bytes()
     traffic = NCU_DRAM_TRAFFIC.get(w.name, {})
@@ -555,8 +645,10 @@ def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e)
         "config": {"workload": w.name, "cameras_per_gpu": w.B, "queries": w.Q, "heads": w.H,
                    "channels": w.C, "levels": [list(x) for x in w.levels], "points": w.P,
                    "depth_bins": w.D, "points_per_gpu_step": w.points,
-                   "l2": "inputs per step (%.0f MB) exceed the 126 MB L2; no explicit flush"
-                         % (fwd_b / 1e6)},
+                   "l2": ("inputs per step (%.0f MB) exceed the 126 MB L2; no explicit flush" % (fwd_b / 1e6))
+                         if fwd_b > 126e6 else
+                         ("inputs per step (%.1f MB) fit in the 126 MB L2 and no flush is made: a "
+                          "parity-sized workload, not a bandwidth measurement" % (fwd_b / 1e6))},
         "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
         "clocks": clocks,
         "gpu_launches": runner.launches_per_step * a.steps,
@@ -575,6 +667,17 @@ def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e)
             "algorithmic_bytes": fwd_b}
         line["roofline_step"] = {"frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak,
                                  "algorithmic_bytes": fwd_b + bwd_b}
+        floor = (extra or {}).get("memory_stream_floor") or {}
+        if "backward_ms" in floor:
+            # floor_ms: the launch's reductions alone at the measured L2 reduction rate (nothing the
+            # kernel does can make them cheaper); stream_ms: all of its gathers and reductions replayed
+            # without arithmetic
+            line["roofline"]["floor_ms"] = floor["backward_reductions_only_ms"]
+            line["roofline"]["frac_of_floor"] = floor["backward_reductions_only_ms"] / bwd_ms
+            line["roofline"]["stream_ms"] = floor["backward_ms"]
+            line["roofline_forward"]["stream_ms"] = floor["forward_ms"]
+        if extra:
+            line["extra"] = extra
         if world == 1 and not a.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w, 1)
     else:

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define DFA3D_ABI_VERSION 1
+#define DFA3D_ABI_VERSION 2
 
 #define DFA3D_OK 0
 #define DFA3D_ERR_INVALID_ARGUMENT (-1) /* null pointer, non-positive size, bad enum, misaligned pointer */
@@ -57,6 +57,16 @@ typedef struct dfa3d_problem {
   int64_t dist_head_stride;  /* elements between heads of one pixel in `dist`: D for (B,N,H,D);
                                 0 for (B,N,D) shared by all heads (then grad_dist is (B,N,D) too,
                                 already summed over heads) */
+  int32_t dist_map_h;        /* 0, 0: `dist` has one row per pixel of `value` (N rows per camera).  */
+  int32_t dist_map_w;        /* h, w > 0: `dist` is ONE map of h x w pixels per camera (h*w rows) that
+                                every level samples with nearest-neighbour indexing -- the depth
+                                network predicts at one resolution and the reference resizes that map
+                                to every feature level with F.interpolate(mode="nearest")
+                                (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/dense_heads/
+                                depth_head.py:273-276); pixel (y, x) of a level of size (H_l, W_l) reads
+                                map pixel (min(floor(y * (float)h / H_l), h-1), min(floor(x * (float)w /
+                                W_l), w-1)), which is that resize.  grad_dist then has the map's layout
+                                and holds the sum over all level pixels that read a map pixel. */
 } dfa3d_problem;
 
 /* ABI version of the loaded library (== DFA3D_ABI_VERSION of the header it was built from). */
@@ -152,6 +162,76 @@ int dfa3d_attn3d_backward(const dfa3d_problem *p, int32_t num_anchors, const voi
                           const float *offsets_depth, const float *logits, const float *grad_out,
                           float *grad_value, float *grad_dist, float *grad_offsets_uv,
                           float *grad_offsets_depth, float *grad_logits, void *stream);
+
+/* The one-stage and the offsets/logits entry points for cameras with DIFFERENT numbers of queries
+ * (BEVFormer: every camera sees its own subset of the BEV queries; the reference pads all of them to the
+ * longest list, spatial_cross_attention.py:707-722).  query_offsets (B+1 int32, device) gives camera b
+ * the packed rows [query_offsets[b], query_offsets[b+1]) of every per-query tensor, which therefore lose
+ * their batch dimension: loc3 (R,H,L,P,3), attn (R,H,L,P), out (R,H*C), ref_points (R,Z,3), ... with
+ * R = query_offsets[B].  p->Q is then only an upper bound of the queries of any one camera (it sizes the
+ * launch); value / dist and their gradients keep their (B, N, ...) layout.  Everything else is as in
+ * the entry point of the same name without the suffix. */
+int dfa3d_fused_forward_ragged(const dfa3d_problem *p, const int32_t *query_offsets, const void *value,
+                               const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                               const float *loc3, const float *attn, float *out,
+                               float *depth_score_out, void *stream);
+int dfa3d_fused_backward_ragged(const dfa3d_problem *p, const int32_t *query_offsets, const void *value,
+                                const void *dist, const int64_t *shapes3, const int64_t *level_start,
+                                const float *loc3, const float *attn, const float *grad_out,
+                                float *grad_value, float *grad_dist, float *grad_loc3,
+                                float *grad_attn, void *stream);
+int dfa3d_attn3d_forward_ragged(const dfa3d_problem *p, int32_t num_anchors,
+                                const int32_t *query_offsets, const void *value, const void *dist,
+                                const int64_t *shapes3, const int64_t *level_start,
+                                const float *ref_points, const float *offsets_uv,
+                                const float *offsets_depth, const float *logits, float *out,
+                                void *stream);
+int dfa3d_attn3d_backward_ragged(const dfa3d_problem *p, int32_t num_anchors,
+                                 const int32_t *query_offsets, const void *value, const void *dist,
+                                 const int64_t *shapes3, const int64_t *level_start,
+                                 const float *ref_points, const float *offsets_uv,
+                                 const float *offsets_depth, const float *logits, const float *grad_out,
+                                 float *grad_value, float *grad_dist, float *grad_offsets_uv,
+                                 float *grad_offsets_depth, float *grad_logits, void *stream);
+
+/* Per-camera re-batching of the BEV queries.  Replaces the host loops of
+ * SpatialCrossAttention_DFA3D.forward (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/
+ * spatial_cross_attention.py:700-722 build the per-camera index lists with nonzero() and copy the
+ * queries / reference points into zero-padded (bs, cams, max_len, ...) tensors; :741-748 add the
+ * per-camera results back into BEV order and divide by the number of cameras that see each query).
+ *
+ * dfa3d_rebatch_plan: bev_mask (cams, bs, Q, Z) bytes (0 / non-0), device.  Camera i sees query q when any
+ * of the Z entries of batch element 0 is set (:703-705).  Outputs (device, written entirely):
+ *   counts (cams)            queries seen per camera
+ *   offsets (cams+1)         exclusive prefix sums; T = offsets[cams] rows per batch element
+ *   op_offsets (bs*cams+1)   j*T + offsets[i] at index j*cams + i: the query_offsets of the *_ragged
+ *                            entry points for B = bs*cams
+ *   packed_query, packed_camera (capacity cams*Q each; the first T entries are written)
+ *                            BEV query and camera of packed row p, cameras in order, queries ascending
+ *   row_of (cams, Q)         packed row of (camera, query) or -1
+ *   inv_count (bs, Q)        1 / max(1, cameras that see q in batch element j)          (:745-747)
+ * No host synchronisation; the caller learns T by reading offsets[cams] when it needs exact sizes. */
+int dfa3d_rebatch_plan(const uint8_t *bev_mask, int32_t cams, int32_t bs, int32_t Q, int32_t Z,
+                       int32_t *counts, int32_t *offsets, int32_t *op_offsets, int32_t *packed_query,
+                       int32_t *packed_camera, int32_t *row_of, float *inv_count, void *stream);
+
+/* dst[j*T + p, :] = scale[j, q] * src[camera*src_camera_stride + j*src_batch_stride + q, :] with
+ * q = packed_query[p], camera = packed_camera[p]; rows of `width` floats; strides in rows (0 = the
+ * source is shared by all cameras / batch elements); scale (bs, Q) or null.  rows_bound >= bs*T sizes
+ * the launch (bs*cams*Q always suffices).  Replaces :710-722; with scale = inv_count it is also the
+ * backward of dfa3d_rebatch_combine. */
+int dfa3d_rebatch_gather(const float *src, const int32_t *packed_query, const int32_t *packed_camera,
+                         const int32_t *offsets, int32_t cams, int32_t bs, int32_t Q, int32_t width,
+                         int64_t src_camera_stride, int64_t src_batch_stride, const float *scale,
+                         float *dst, int64_t rows_bound, void *stream);
+
+/* dst[j, q, :] = scale[j, q] * sum over the cameras i that see q of src[j*T + row_of[i, q], :]
+ * (zeros where no camera sees q; every element of dst is written; no atomics: each output row is
+ * formed by one thread group).  Replaces :741-748; without scale it is the backward of
+ * dfa3d_rebatch_gather for a source shared by all cameras. */
+int dfa3d_rebatch_combine(const float *src, const int32_t *row_of, const int32_t *offsets, int32_t cams,
+                          int32_t bs, int32_t Q, int32_t width, const float *scale, float *dst,
+                          void *stream);
 
 #ifdef __cplusplus
 }

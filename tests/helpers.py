@@ -1,4 +1,6 @@
 """Shared helpers of the parity tests."""
+import os
+
 import numpy as np
 import torch
 
@@ -17,6 +19,19 @@ def to_np(t):
     return np.asarray(t, dtype=np.float64)
 
 
+# Filled by assert_close when the environment variable DFA3D_TOL_STATS names a file: per comparison,
+# how many elements pass only thanks to the absolute term of the tolerance (written at session end by
+# conftest.py).  Lets the share of elements that lean on `atol_frac * max|ref|` be stated with numbers.
+TOL_STATS = []
+
+
+def count_out_of_tolerance(got, ref, rtol, atol=0.0, atol_frac=0.0):
+    """Number of elements with |got - ref| > rtol*|ref| + atol + atol_frac*max|ref|."""
+    got, ref = to_np(got), to_np(ref)
+    tol = rtol * np.abs(ref) + atol + atol_frac * (np.abs(ref).max() if ref.size else 0.0)
+    return int((np.abs(got - ref) > tol).sum())
+
+
 def assert_close(name, got, ref, rtol, atol=0.0, atol_frac=0.0):
     got, ref = to_np(got), to_np(ref)
     assert got.shape == ref.shape, f"{name}: shape {got.shape} vs {ref.shape}"
@@ -24,6 +39,12 @@ def assert_close(name, got, ref, rtol, atol=0.0, atol_frac=0.0):
     tol = rtol * np.abs(ref) + atol + atol_frac * (np.abs(ref).max() if ref.size else 0.0)
     err = np.abs(got - ref)
     bad = err > tol
+    if os.environ.get("DFA3D_TOL_STATS"):
+        TOL_STATS.append({"test": os.environ.get("PYTEST_CURRENT_TEST", ""), "tensor": name,
+                          "elements": int(err.size), "beyond_relative_term": int((err > rtol * np.abs(ref)).sum()),
+                          "failed": int(bad.sum()), "rtol": rtol, "atol": atol, "atol_frac": atol_frac,
+                          "max_abs_ref": float(np.abs(ref).max()) if ref.size else 0.0,
+                          "max_abs_err": float(err.max()) if err.size else 0.0})
     if bad.any():
         i = np.unravel_index(np.argmax(err - tol), err.shape)
         raise AssertionError(

@@ -21,7 +21,9 @@ def test_header_declares_the_expected_entry_points():
     for n in ("dfa3d_depth_score_forward", "dfa3d_depth_score_backward", "dfa3d_wms_attn_forward",
               "dfa3d_wms_attn_backward", "dfa3d_fused_forward", "dfa3d_fused_backward",
               "dfa3d_attn3d_forward", "dfa3d_attn3d_backward", "dfa3d_msda_forward",
-              "dfa3d_msda_backward",
+              "dfa3d_msda_backward", "dfa3d_fused_forward_ragged", "dfa3d_fused_backward_ragged",
+              "dfa3d_attn3d_forward_ragged", "dfa3d_attn3d_backward_ragged", "dfa3d_rebatch_plan",
+              "dfa3d_rebatch_gather", "dfa3d_rebatch_combine",
               "dfa3d_last_error", "dfa3d_abi_version"):
         assert n in names
 
@@ -35,15 +37,16 @@ def test_library_exports_every_declared_symbol(lib_built):
 def test_binding_table_matches_header(lib_built):
     from dfa3d_b200 import _lib
     declared = set(declared_symbols()) - {"dfa3d_last_error", "dfa3d_abi_version"}
-    bound = set(_lib.ENTRY_POINTS) | set(_lib.ENTRY_POINTS_WITH_ANCHORS)
+    bound = set(_lib.ENTRY_POINTS) | set(_lib.ENTRY_POINTS_WITH_ANCHORS) | set(_lib.PLAIN_ENTRY_POINTS)
     assert declared <= bound, declared - bound
     assert _lib.load().dfa3d_abi_version() == _lib.ABI_VERSION
 
 
 def test_problem_struct_layout():
     from dfa3d_b200 import _lib
-    assert ctypes.sizeof(_lib.Problem) == 10 * 4 + 8
+    assert ctypes.sizeof(_lib.Problem) == 10 * 4 + 8 + 2 * 4
     assert _lib.Problem.dist_head_stride.offset == 40
+    assert _lib.Problem.dist_map_h.offset == 48 and _lib.Problem.dist_map_w.offset == 52
 
 
 def test_validation_returns_codes_not_crashes(lib_built):
@@ -71,9 +74,25 @@ def test_validation_returns_codes_not_crashes(lib_built):
     # empty problem: nothing to do, OK without touching the pointers
     empty = _lib.Problem(0, 4, 1, 4, 2, 1, 0, 1, 0, 0, 2)
     for name, n in _lib.ENTRY_POINTS.items():
-        assert getattr(lib, name)(ctypes.byref(empty), *([None] * n)) == 0, name
+        if name.endswith("_ragged"):     # the offset table is required even for an empty problem
+            assert getattr(lib, name)(ctypes.byref(empty), *([None] * n)) == -1, name
+            assert getattr(lib, name)(ctypes.byref(empty), 16, *([None] * (n - 1))) == 0, name
+        else:
+            assert getattr(lib, name)(ctypes.byref(empty), *([None] * n)) == 0, name
     for name, n in _lib.ENTRY_POINTS_WITH_ANCHORS.items():
-        assert getattr(lib, name)(ctypes.byref(empty), 1, *([None] * n)) == 0, name
+        if name.endswith("_ragged"):
+            assert getattr(lib, name)(ctypes.byref(empty), 1, *([None] * n)) == -1, name
+            assert getattr(lib, name)(ctypes.byref(empty), 1, 16, *([None] * (n - 1))) == 0, name
+        else:
+            assert getattr(lib, name)(ctypes.byref(empty), 1, *([None] * n)) == 0, name
+    # re-batching entry points: sizes are checked before any pointer is used
+    assert lib.dfa3d_rebatch_plan(None, 0, 1, 4, 1, *([None] * 8)) == -1
+    assert lib.dfa3d_rebatch_plan(None, 2, 1, 4, 1, *([None] * 8)) == -1
+    assert b"counts" in lib.dfa3d_last_error()
+    assert lib.dfa3d_rebatch_gather(None, None, None, None, 2, 1, 4, 8, 0, 4, None, None, 0, None) == 0
+    assert lib.dfa3d_rebatch_gather(None, None, None, None, 2, 1, 4, 0, 0, 4, None, None, 8, None) == -1
+    assert lib.dfa3d_rebatch_combine(None, None, None, 2, 1, 0, 8, None, None, None) == 0
+    assert lib.dfa3d_rebatch_combine(None, None, None, 2, 1, 4, 8, None, None, None) == -1
     # the anchors must divide the points per level
     assert lib.dfa3d_attn3d_forward(ctypes.byref(ok), 3, *([None] * 10)) == -1
     assert b"num_anchors" in lib.dfa3d_last_error()

@@ -183,9 +183,11 @@ def test_matches_reference_cuda_golden(M, path):
     check_against(got, ref, False)
 
 
-@pytest.mark.parametrize("name", ["cfg0", "cfg1", "cfg2"])
+@pytest.mark.parametrize("name", ["cfg0", "cfg1", "cfg2", "cfg4op"])
 def test_matches_reference_op_live(M, REF, name):
-    """The reference's unmodified CUDA op (built for sm_100a), same tensors, same GPU."""
+    """The reference's unmodified CUDA op (built for sm_100a), same tensors, same GPU.  cfg4op has
+    D = 118 depth bins: not a multiple of 4, so the unaligned branches of the depth-pair loads and
+    reductions run at full size here."""
     w = wl.WORKLOADS[name]
     d = wl.make_inputs(w, head_repeat=False)
     t = {k: v.to(DEV) for k, v in d.items()}
@@ -206,6 +208,115 @@ def test_matches_reference_op_live(M, REF, name):
     assert_close("grad_dist", mine[1].grad, leaves[1].grad.sum(2), **BWD)
     assert_close("grad_loc", mine[2].grad, leaves[2].grad, **BWD)
     assert_close("grad_attn", mine[3].grad, leaves[3].grad, **BWD)
+
+
+@pytest.mark.parametrize("name", ["cfg0", "cfg1"])
+def test_two_stage_api_matches_reference_op_live(M, REF, name):
+    """MultiScaleDepthScoreSampleFunction -> WeightedMultiScaleDeformableAttnFunction against the
+    reference's own two Functions (DFA3D/dfa3D/ops/multi_scale_3D_deform_attn.py:22-145) with the
+    gradient flowing through depth_score, at C = 32 (the vector kernels in "depth score given" mode)."""
+    w = wl.WORKLOADS[name]
+    d = wl.make_inputs(w, head_repeat=True)
+    t = {k: v.to(DEV) for k, v in d.items()}
+    shapes2, go = t["shapes"][:, :2].contiguous(), t["grad_out"]
+
+    def two_stage(ns):
+        dist = t["dist"].clone().requires_grad_(True)
+        value = t["value"].clone().requires_grad_(True)
+        loc = t["loc"].clone().requires_grad_(True)
+        attn = t["attn"].clone().requires_grad_(True)
+        ds = ns.MultiScaleDepthScoreSampleFunction.apply(dist, t["shapes"], t["lsi"], loc, 64)
+        ds.retain_grad()
+        out = ns.WeightedMultiScaleDeformableAttnFunction.apply(
+            value, shapes2, t["lsi"], loc[..., :2].contiguous(), attn, ds, 64)
+        out.backward(go)
+        return dict(ds=ds, out=out, grad_ds=ds.grad, grad_value=value.grad, grad_dist=dist.grad,
+                    grad_loc=loc.grad, grad_attn=attn.grad)
+
+    ref, got = two_stage(REF), two_stage(M)
+    assert_close("depth_score", got["ds"], ref["ds"], **FWD)
+    assert_close("out", got["out"], ref["out"], **FWD)
+    for k in ("grad_ds", "grad_value", "grad_dist", "grad_loc", "grad_attn"):
+        assert_close(k, got[k], ref[k], **BWD)
+
+
+def test_two_stage_grad_depth_score_matches_reference_cuda_golden(M):
+    """grad_depth_score of the attention backward against the value the reference's CUDA op produced
+    for cfg0 (stored in the golden file by tests/golden/make_golden.py)."""
+    z = np.load(os.path.join(GOLD, "cfg0_ref_cuda_f32.npz"))
+    d = wl.make_inputs(wl.WORKLOADS["cfg0"], head_repeat=True)
+    t = {k: v.to(DEV) for k, v in d.items()}
+    ds = torch.from_numpy(z["ds"]).to(DEV).requires_grad_(True)
+    value = t["value"].clone().requires_grad_(True)
+    out = M.WeightedMultiScaleDeformableAttnFunction.apply(
+        value, t["shapes"][:, :2].contiguous(), t["lsi"], t["loc"][..., :2].contiguous(), t["attn"], ds, 64)
+    out.backward(t["grad_out"])
+    assert_close("out", out, z["out"], **FWD)
+    assert_close("grad_ds", ds.grad, z["grad_ds"], **BWD)
+    assert_close("grad_value", value.grad, z["grad_value"], **BWD)
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg4op"])
+def test_benchmark_shape_camera_matches_oracle(M, name, record_property):
+    """Element-wise check at the benchmark shapes: one camera of cfg2 (fp32), cfg3 (bf16 storage of
+    value and dist; the oracle consumes the same bf16-rounded numbers in fp32) and cfg4op (D = 118),
+    all six outputs against the C oracle.  bf16 storage is held to the 1e-2 relative bound it is
+    allowed and, like fp32, to the fp32 tolerances; the number of elements outside the fp32 tolerances
+    is recorded."""
+    from dfa3d_b200 import ext
+    from helpers import count_out_of_tolerance
+    w = wl.WORKLOADS[name].with_(B=1)
+    bf16 = w.value_dtype == "bf16"
+    d = wl.make_inputs(w, head_repeat=True)
+    ref = oracle_all(d, np.float32)
+    t = {k: v.to(DEV) for k, v in d.items()}
+    value = t["value"].bfloat16() if bf16 else t["value"]
+    for shared in (True, False):
+        dist32 = t["dist"][:, :, 0].contiguous() if shared else t["dist"]
+        dist = dist32.bfloat16() if bf16 else dist32
+        out, ds = ext.dfa3d_fused_forward(value, dist, t["shapes"], t["lsi"], t["loc"], t["attn"], 64)
+        gv = torch.zeros_like(t["value"]); gd = torch.zeros_like(dist32)
+        gl = torch.empty_like(t["loc"]); ga = torch.empty_like(t["attn"])
+        ext.dfa3d_fused_backward(value, dist, t["shapes"], t["lsi"], t["loc"], t["attn"], t["grad_out"], gv,
+                                 gd, gl, ga, 64)
+        got = dict(out=out, ds=ds, grad_value=gv, grad_dist=gd, grad_loc=gl, grad_attn=ga)
+        if bf16:
+            check_against(got, ref, shared, fwd=BF16, bwd=BF16)
+        misses = {}
+        for k, tol in (("out", FWD), ("ds", FWD), ("grad_value", BWD), ("grad_dist", BWD),
+                       ("grad_loc", BWD), ("grad_attn", BWD)):
+            r = ref[k].sum(2) if (k == "grad_dist" and shared) else ref[k]
+            misses[k] = count_out_of_tolerance(got[k], r, **tol)
+        record_property(f"fp32_tolerance_misses_{'shared' if shared else 'per_head'}", misses)
+        print(f"{name} ({'shared' if shared else 'per-head'} dist): elements outside the fp32 tolerances: {misses}")
+        check_against(got, ref, shared)
+
+
+def test_bf16_leaves_through_autograd(M):
+    """The one-stage Function called with bfloat16 value / value_dpt_dist LEAVES, as a user would.  The
+    kernels produce float32 gradients; autograd hands a leaf a gradient of the leaf's own dtype, so
+    value.grad and value_dpt_dist.grad arrive rounded to bfloat16 (the float32 gradients are available
+    through ext.dfa3d_fused_backward).  Locations and attention weights are float32 leaves and get
+    float32 gradients."""
+    w = wl.WORKLOADS["odd"].with_(C=32, value_dtype="bf16", seed=31)
+    d = wl.make_inputs(w, head_repeat=True)
+    ref = oracle_all(d, np.float32)
+    value = d["value"].to(DEV).bfloat16().requires_grad_(True)
+    dist = d["dist"].to(DEV).bfloat16().requires_grad_(True)
+    loc = d["loc"].to(DEV).requires_grad_(True)
+    attn = d["attn"].to(DEV).requires_grad_(True)
+    out, ds = M.MultiScale3DDeformableAttnFunction.apply(value, dist, d["shapes"].to(DEV), d["lsi"].to(DEV),
+                                                         loc, attn, 64)
+    out.backward(d["grad_out"].to(DEV))
+    assert out.dtype == torch.float32 and ds.dtype == torch.float32
+    assert value.grad.dtype == torch.bfloat16 and dist.grad.dtype == torch.bfloat16
+    assert loc.grad.dtype == torch.float32 and attn.grad.dtype == torch.float32
+    assert_close("out", out, ref["out"], **FWD)
+    assert_close("grad_loc", loc.grad, ref["grad_loc"], **BWD)
+    assert_close("grad_attn", attn.grad, ref["grad_attn"], **BWD)
+    # bf16 rounding of the gradient: half an ulp = 2^-9 relative
+    assert_close("grad_value", value.grad.float(), ref["grad_value"], rtol=4e-3, atol_frac=1e-5)
+    assert_close("grad_dist", dist.grad.float(), ref["grad_dist"], rtol=4e-3, atol_frac=1e-5)
 
 
 @pytest.mark.parametrize("name,bf16", [("cfg2", False), ("cfg3", True), ("cfg4op", False)])

@@ -39,19 +39,32 @@ def test_assemble_sampling_locations_matches_loops():
                         torch.testing.assert_close(got[b, q, h, l, j], exp)
 
 
-def test_rebatch_indexes_matches_reference_loops():
-    g = torch.Generator().manual_seed(1)
-    cams, bs, Q, Z = 3, 2, 17, 4
-    mask = torch.rand(cams, bs, Q, Z, generator=g) > 0.8
-    mask[2] = False                       # a camera that sees nothing
-    index, valid = modules.SpatialCrossAttention_DFA3D.rebatch_indexes(mask)
-    lens = []
-    for i in range(cams):                 # spatial_cross_attention.py:703-707
-        idx = mask[i][0].sum(-1).nonzero().squeeze(-1)
-        lens.append(len(idx))
-        assert index[i, :len(idx)].tolist() == idx.tolist()
-        assert valid[i].tolist() == [True] * len(idx) + [False] * (index.shape[1] - len(idx))
-    assert index.shape[1] == max(lens)
+def test_point_sampling_matches_per_point_projection():
+    """modules.point_sampling (encoder.py:421-476) against a projection written point by point."""
+    g = torch.Generator().manual_seed(4)
+    bs, cams, Q, Z = 2, 3, 11, 4
+    ref = torch.rand(bs, Z, Q, 3, generator=g)
+    pc_range = (-51.2, -51.2, -5.0, 51.2, 51.2, 3.0)
+    d_bound = (2.0, 58.0, 0.5)
+    img_shape = (928, 1600)
+    lidar2img = torch.randn(bs, cams, 4, 4, generator=g) * 50
+    cam_pts, mask = modules.point_sampling(ref, pc_range, lidar2img, img_shape, d_bound)
+    assert cam_pts.shape == (cams, bs, Q, Z, 3) and mask.shape == (cams, bs, Q, Z)
+    assert mask.dtype == torch.bool
+    for j in range(bs):
+        for i in range(cams):
+            for q in range(Q):
+                for z in range(Z):
+                    p = ref[j, z, q]
+                    world = torch.tensor([p[0] * 102.4 - 51.2, p[1] * 102.4 - 51.2, p[2] * 8.0 - 5.0, 1.0])
+                    c = lidar2img[j, i] @ world
+                    front = c[2] > 1e-5
+                    x = c[0] / max(c[2].item(), 1e-5) / img_shape[1]
+                    y = c[1] / max(c[2].item(), 1e-5) / img_shape[0]
+                    dz = (c[2] - 2.0) / 56.0
+                    got = cam_pts[i, j, q, z]
+                    torch.testing.assert_close(got, torch.stack([x, y, dz]), rtol=1e-4, atol=1e-4)
+                    assert bool(mask[i, j, q, z]) == bool(front and 0 < x < 1 and 0 < y < 1)
 
 
 def test_module_initialisation_follows_reference():
