@@ -417,4 +417,55 @@ int dfa3d_rebatch_combine(const float *src, const int32_t *row_of, const int32_t
                 "dfa3d_rebatch_combine launch");
 }
 
+// ---- depth-distribution producer --------------------------------------------------------------
+static int check_producer(int32_t B, int32_t D, int32_t map_h, int32_t map_w, int32_t shape_stride,
+                          int32_t L, int32_t N, int32_t activation) {
+  if (B < 0 || N < 0) return fail(DFA3D_ERR_INVALID_ARGUMENT, "B and N must be >= 0");
+  if (D <= 0 || map_h <= 0 || map_w <= 0 || L <= 0)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "D, map_h, map_w, L must be positive (got %d %d %d %d)", D, map_h,
+                map_w, L);
+  if (D > dfa3d::dist_producer_max_bins())
+    return fail(DFA3D_ERR_UNSUPPORTED, "D=%d exceeds the producer's limit of %d bins", D,
+                dfa3d::dist_producer_max_bins());
+  if (L > DFA3D_MAX_LEVELS) return fail(DFA3D_ERR_UNSUPPORTED, "L=%d exceeds DFA3D_MAX_LEVELS", L);
+  if (shape_stride != 2 && shape_stride != 3)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "shape_stride must be 2 or 3 (got %d)", shape_stride);
+  if (activation != DFA3D_ACT_SOFTMAX && activation != DFA3D_ACT_SIGMOID)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "activation %d is not a DFA3D_ACT_*", activation);
+  if ((long long)N * D >= (1LL << 31) || (long long)D * map_h * map_w >= (1LL << 31))
+    return fail(DFA3D_ERR_UNSUPPORTED, "N*D and D*map_h*map_w must stay below 2^31");
+  return DFA3D_OK;
+}
+
+int dfa3d_dist_from_logits(const float *logits, int32_t B, int32_t D, int32_t map_h, int32_t map_w,
+                           const int64_t *spatial_shapes, int32_t shape_stride,
+                           const int64_t *level_start, int32_t L, int32_t N, int32_t activation,
+                           int32_t dist_dtype, void *dist, void *stream) {
+  if (int rc = check_producer(B, D, map_h, map_w, shape_stride, L, N, activation)) return rc;
+  if (dist_dtype != DFA3D_DTYPE_F32 && dist_dtype != DFA3D_DTYPE_BF16)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "dist_dtype %d is not a DFA3D_DTYPE_*", dist_dtype);
+  if (B == 0 || N == 0) return DFA3D_OK;
+  REQUIRE_PTR(logits); REQUIRE_PTR(spatial_shapes); REQUIRE_PTR(level_start); REQUIRE_PTR(dist);
+  return finish(dfa3d::launch_dist_from_logits(logits, spatial_shapes, shape_stride, level_start, dist,
+                                               dist_dtype == DFA3D_DTYPE_BF16, B, D, map_h, map_w, N, L,
+                                               activation == DFA3D_ACT_SIGMOID, (cudaStream_t)stream),
+                "dfa3d_dist_from_logits launch");
+}
+
+int dfa3d_dist_from_logits_backward(const float *logits, int32_t B, int32_t D, int32_t map_h,
+                                    int32_t map_w, const int64_t *spatial_shapes, int32_t shape_stride,
+                                    const int64_t *level_start, int32_t L, int32_t N,
+                                    int32_t activation, const float *grad_dist, float *grad_logits,
+                                    void *stream) {
+  if (int rc = check_producer(B, D, map_h, map_w, shape_stride, L, N, activation)) return rc;
+  if (B == 0) return DFA3D_OK;
+  REQUIRE_PTR(logits); REQUIRE_PTR(spatial_shapes); REQUIRE_PTR(level_start); REQUIRE_PTR(grad_logits);
+  if (N > 0) REQUIRE_PTR(grad_dist);
+  return finish(dfa3d::launch_dist_from_logits_backward(logits, spatial_shapes, shape_stride, level_start,
+                                                        grad_dist, grad_logits, B, D, map_h, map_w, N, L,
+                                                        activation == DFA3D_ACT_SIGMOID,
+                                                        (cudaStream_t)stream),
+                "dfa3d_dist_from_logits_backward launch");
+}
+
 }  // extern "C"

@@ -22,4 +22,13 @@ cudaError_t launch_rebatch_gather(const float *src, const int32_t *packed_query,
 cudaError_t launch_rebatch_combine(const float *src, const int32_t *row_of, const int32_t *offsets,
                                    int cams, int bs, int Q, int W, const float *scale, float *dst,
                                    cudaStream_t s);
+// depth-distribution producer (dfa3d_dist_producer.cu)
+int dist_producer_max_bins();
+cudaError_t launch_dist_from_logits(const float *logits, const int64_t *shapes, int shape_stride,
+                                    const int64_t *lsi, void *dist, bool dist_bf16, int B, int D, int hs,
+                                    int ws, int N, int L, bool sigmoid, cudaStream_t s);
+cudaError_t launch_dist_from_logits_backward(const float *logits, const int64_t *shapes, int shape_stride,
+                                             const int64_t *lsi, const float *grad_dist,
+                                             float *grad_logits, int B, int D, int hs, int ws, int N,
+                                             int L, bool sigmoid, cudaStream_t s);
 }  // namespace dfa3d

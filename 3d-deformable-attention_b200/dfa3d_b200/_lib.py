@@ -61,7 +61,12 @@ PLAIN_ENTRY_POINTS = {
     "dfa3d_rebatch_gather": [ctypes.c_void_p] * 4 + [_I32] * 4 + [_I64, _I64] + [ctypes.c_void_p] * 2
                             + [_I64, ctypes.c_void_p],
     "dfa3d_rebatch_combine": [ctypes.c_void_p] * 3 + [_I32] * 4 + [ctypes.c_void_p] * 3,
+    "dfa3d_dist_from_logits": [ctypes.c_void_p] + [_I32] * 4 + [ctypes.c_void_p, _I32, ctypes.c_void_p]
+                              + [_I32] * 4 + [ctypes.c_void_p] * 2,
+    "dfa3d_dist_from_logits_backward": [ctypes.c_void_p] + [_I32] * 4 + [ctypes.c_void_p, _I32, ctypes.c_void_p]
+                                       + [_I32] * 3 + [ctypes.c_void_p] * 3,
 }
+ACT_SOFTMAX, ACT_SIGMOID = 0, 1
 
 _lib = None
 

@@ -57,6 +57,21 @@ def _stream(t):
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+def _map(dist_map):
+    """dist_map: None, or (h, w) of the single map all levels read with nearest indexing."""
+    if dist_map is None:
+        return 0, 0
+    mh, mw = int(dist_map[0]), int(dist_map[1])
+    if mh <= 0 or mw <= 0:
+        raise RuntimeError(f"dist_map must be two positive sizes, got {dist_map}")
+    return mh, mw
+
+
+def _dist_rows_ok(Nd, N, dist_map):
+    mh, mw = _map(dist_map)
+    return Nd == (mh * mw if mh else N)
+
+
 def _dist_problem(dist, H):
     """dist is (B,N,H,D), or (B,N,D) shared by all heads.  Returns (B, N, D, head_stride)."""
     if dist.dim() == 4:
@@ -79,6 +94,17 @@ def _level_table(shapes, lsi, L, width):
                            f"{lsi.numel()}")
 
 
+def _level_pixels(n_dist_rows, dist_map, shapes):
+    """N of the problem descriptor for the depth-only entry points: the rows of dist, or -- with a single
+    map -- the pixels of all levels (corner pixels are bounded by it)."""
+    if dist_map is None:
+        return n_dist_rows
+    mh, mw = _map(dist_map)
+    if n_dist_rows != mh * mw:
+        raise RuntimeError(f"value has {n_dist_rows} rows per camera, dist_map {mh}x{mw} needs {mh * mw}")
+    return int((shapes[:, 0] * shapes[:, 1]).sum())     # one read-back; depth-only API with a map
+
+
 def _loc_dims(loc, last):
     if loc.dim() != 6 or loc.shape[-1] != last:
         raise RuntimeError(f"sampling_locations must be (B,Q,H,L,P,{last}), got {tuple(loc.shape)}")
@@ -87,8 +113,9 @@ def _loc_dims(loc, last):
 
 # ------------------------------------------------------------------------------------------------
 def ms_depth_score_sample_forward(value, value_spatial_shapes, value_level_start_index,
-                                  sampling_locations, im2col_step):
-    """`value` is the depth distribution (B,N,H,D) [or (B,N,D)]; returns depth_score (B,Q,H,L,P,4)."""
+                                  sampling_locations, im2col_step, dist_map=None):
+    """`value` is the depth distribution (B,N,H,D) [or (B,N,D)]; returns depth_score (B,Q,H,L,P,4).
+    dist_map=(h, w): `value` is one h x w map per camera that every level reads with nearest indexing."""
     dist = value
     _chk(dist, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
     _chk(value_level_start_index, "level_start_index", _I64)
@@ -101,7 +128,8 @@ def ms_depth_score_sample_forward(value, value_spatial_shapes, value_level_start
     _level_table(value_spatial_shapes, value_level_start_index, L, 3)
     _step_check(B, im2col_step)
     out = torch.empty((B, Q, H, L, P, 4), dtype=torch.float32, device=dist.device)
-    pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs)
+    N = _level_pixels(N, dist_map, value_spatial_shapes)
+    pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs, *_map(dist_map))
     with torch.cuda.device(dist.device):
         _lib.call("dfa3d_depth_score_forward", pr, _ptr(dist), _ptr(value_spatial_shapes),
                   _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(out), _stream(dist))
@@ -110,7 +138,7 @@ def ms_depth_score_sample_forward(value, value_spatial_shapes, value_level_start
 
 def ms_depth_score_sample_backward(value, value_spatial_shapes, value_level_start_index,
                                    sampling_locations, grad_output, grad_value, grad_sampling_loc,
-                                   im2col_step):
+                                   im2col_step, dist_map=None):
     """Accumulates into grad_value (layout of `value`, float32, caller-zeroed) and overwrites
     grad_sampling_loc (B,Q,H,L,P,3) with (0, 0, dL/dz)."""
     dist = value
@@ -129,7 +157,8 @@ def ms_depth_score_sample_backward(value, value_spatial_shapes, value_level_star
         raise RuntimeError("inconsistent shapes between value and sampling_loc")
     _level_table(value_spatial_shapes, value_level_start_index, L, 3)
     _step_check(B, im2col_step)
-    pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs)
+    N = _level_pixels(N, dist_map, value_spatial_shapes)
+    pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs, *_map(dist_map))
     with torch.cuda.device(dist.device):
         _lib.call("dfa3d_depth_score_backward", pr, _ptr(dist), _ptr(value_spatial_shapes),
                   _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(grad_output),
@@ -256,7 +285,7 @@ def ms_deform_attn_backward(value, value_spatial_shapes, value_level_start_index
 # one-launch fused entry points (no counterpart in the reference's extension; they serve the
 # one-stage autograd Function)
 # ------------------------------------------------------------------------------------------------
-def _fused_problem(value, dist, shapes3, lsi, loc3, attn):
+def _fused_problem(value, dist, shapes3, lsi, loc3, attn, dist_map=None):
     _chk(value, "value", _VAL); _chk(dist, "value_dpt_dist", _VAL)
     _chk(shapes3, "spatial_shapes", _I64); _chk(lsi, "level_start_index", _I64)
     _chk(loc3, "sampling_loc", _F32); _chk(attn, "attn_weight", _F32)
@@ -264,22 +293,25 @@ def _fused_problem(value, dist, shapes3, lsi, loc3, attn):
     B, N, H, C = value.shape
     Bq, Q, Hq, L, P = _loc_dims(loc3, 3)
     Bd, Nd, D, hs = _dist_problem(dist, H)
-    if (Bq, Hq) != (B, H) or (Bd, Nd) != (B, N) or tuple(shapes3.shape) != (L, 3) \
+    if (Bq, Hq) != (B, H) or Bd != B or not _dist_rows_ok(Nd, N, dist_map) or tuple(shapes3.shape) != (L, 3) \
             or tuple(attn.shape) != (B, Q, H, L, P):
         raise RuntimeError("inconsistent shapes between value, value_dpt_dist, spatial_shapes (L,3), "
                            "sampling_loc and attn_weight")
     _level_table(shapes3, lsi, L, 3)
-    return _lib.Problem(B, N, H, C, D, L, Q, P, _dt(value), _dt(dist), hs), (B, Q, H, L, P, C)
+    return (_lib.Problem(B, N, H, C, D, L, Q, P, _dt(value), _dt(dist), hs, *_map(dist_map)),
+            (B, Q, H, L, P, C))
 
 
 def dfa3d_fused_forward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                         sampling_locations, attention_weights, im2col_step, need_depth_score=True,
-                        out=None):
+                        out=None, dist_map=None):
     """Returns (output (B,Q,H*C), depth_score (B,Q,H,L,P,4) or None).  `out`, if given, is a
-    preallocated float32 (B,Q,H*C) tensor that receives the output (every element is written)."""
+    preallocated float32 (B,Q,H*C) tensor that receives the output (every element is written).
+    dist_map=(h, w): value_dpt_dist is ONE h x w map per camera, (B, h*w, D) [or (B, h*w, H, D)], read by
+    every level with nearest-neighbour indexing instead of one resized copy per level."""
     pr, (B, Q, H, L, P, C) = _fused_problem(value, value_dpt_dist, value_spatial_shapes,
                                             value_level_start_index, sampling_locations,
-                                            attention_weights)
+                                            attention_weights, dist_map)
     _step_check(B, im2col_step)
     dev = value.device
     if out is None:
@@ -300,12 +332,13 @@ def dfa3d_fused_forward(value, value_dpt_dist, value_spatial_shapes, value_level
 
 def dfa3d_fused_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                          sampling_locations, attention_weights, grad_output, grad_value,
-                         grad_value_dpt_dist, grad_sampling_loc, grad_attn_weight, im2col_step):
+                         grad_value_dpt_dist, grad_sampling_loc, grad_attn_weight, im2col_step,
+                         dist_map=None):
     """Accumulates into grad_value and grad_value_dpt_dist (float32, caller-zeroed); overwrites
     grad_sampling_loc (B,Q,H,L,P,3) and grad_attn_weight."""
     pr, (B, Q, H, L, P, C) = _fused_problem(value, value_dpt_dist, value_spatial_shapes,
                                             value_level_start_index, sampling_locations,
-                                            attention_weights)
+                                            attention_weights, dist_map)
     for t, n in ((grad_output, "grad_output"), (grad_value, "grad_value"),
                  (grad_value_dpt_dist, "grad_value_dpt_dist"), (grad_sampling_loc, "grad_sampling_loc"),
                  (grad_attn_weight, "grad_attn_weight")):
@@ -330,7 +363,7 @@ def dfa3d_fused_backward(value, value_dpt_dist, value_spatial_shapes, value_leve
 # caller-fused entry points: the location assembly and the softmax of the attention module happen
 # inside the kernels (BEVFormer_DFA3D/.../spatial_cross_attention.py:503-538)
 # ------------------------------------------------------------------------------------------------
-def _attn3d_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits):
+def _attn3d_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits, dist_map=None):
     _chk(value, "value", _VAL); _chk(dist, "value_dpt_dist", _VAL)
     _chk(shapes3, "spatial_shapes", _I64); _chk(lsi, "level_start_index", _I64)
     for t, n in ((ref, "reference_points"), (off_uv, "sampling_offsets_uv"),
@@ -347,23 +380,24 @@ def _attn3d_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits):
     Z = ref.shape[2]
     if Z <= 0 or P % Z != 0:
         raise RuntimeError(f"the number of anchors ({Z}) must divide the points per level ({P})")
-    if (Bq, Hq) != (B, H) or (Bd, Nd) != (B, N) or tuple(shapes3.shape) != (L, 3) \
+    if (Bq, Hq) != (B, H) or Bd != B or not _dist_rows_ok(Nd, N, dist_map) or tuple(shapes3.shape) != (L, 3) \
             or off_d.numel() != B * Q * H * L * P or logits.numel() != B * Q * H * L * P:
         raise RuntimeError("inconsistent shapes between value, value_dpt_dist, spatial_shapes (L,3), "
                            "offsets and logits")
     _level_table(shapes3, lsi, L, 3)
-    return _lib.Problem(B, N, H, C, D, L, Q, P, _dt(value), _dt(dist), hs), Z, (B, Q, H, C)
+    return _lib.Problem(B, N, H, C, D, L, Q, P, _dt(value), _dt(dist), hs, *_map(dist_map)), Z, (B, Q, H, C)
 
 
 def dfa3d_attn3d_forward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                          reference_points, sampling_offsets_uv, sampling_offsets_depth,
-                         attention_logits, out=None):
+                         attention_logits, out=None, dist_map=None):
     """value (B,N,H,C); value_dpt_dist (B,N,D)|(B,N,H,D); reference_points (B,Q,Z,3);
     sampling_offsets_uv (B,Q,H,L,P,2) in pixels; sampling_offsets_depth (B,Q,H,L,P) in bins;
     attention_logits (B,Q,H,L*P) before the softmax.  Returns output (B,Q,H*C)."""
     pr, Z, (B, Q, H, C) = _attn3d_problem(value, value_dpt_dist, value_spatial_shapes,
                                           value_level_start_index, reference_points,
-                                          sampling_offsets_uv, sampling_offsets_depth, attention_logits)
+                                          sampling_offsets_uv, sampling_offsets_depth, attention_logits,
+                                          dist_map)
     if out is None:
         out = torch.empty((B, Q, H * C), dtype=torch.float32, device=value.device)
     else:
@@ -382,12 +416,13 @@ def dfa3d_attn3d_forward(value, value_dpt_dist, value_spatial_shapes, value_leve
 def dfa3d_attn3d_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                           reference_points, sampling_offsets_uv, sampling_offsets_depth,
                           attention_logits, grad_output, grad_value, grad_value_dpt_dist,
-                          grad_offsets_uv, grad_offsets_depth, grad_logits):
+                          grad_offsets_uv, grad_offsets_depth, grad_logits, dist_map=None):
     """Accumulates into grad_value / grad_value_dpt_dist (float32, caller-zeroed); overwrites the
     gradients of the offsets and of the logits."""
     pr, Z, (B, Q, H, C) = _attn3d_problem(value, value_dpt_dist, value_spatial_shapes,
                                           value_level_start_index, reference_points,
-                                          sampling_offsets_uv, sampling_offsets_depth, attention_logits)
+                                          sampling_offsets_uv, sampling_offsets_depth, attention_logits,
+                                          dist_map)
     for t, n in ((grad_output, "grad_output"), (grad_value, "grad_value"),
                  (grad_value_dpt_dist, "grad_value_dpt_dist"), (grad_offsets_uv, "grad_offsets_uv"),
                  (grad_offsets_depth, "grad_offsets_depth"), (grad_logits, "grad_logits")):
@@ -416,7 +451,8 @@ def dfa3d_attn3d_backward(value, value_dpt_dist, value_spatial_shapes, value_lev
 _I32 = (torch.int32,)
 
 
-def _ragged_common(value, dist, shapes3, lsi, query_offsets, max_queries, rows, per_row, names):
+def _ragged_common(value, dist, shapes3, lsi, query_offsets, max_queries, rows, per_row, names,
+                   dist_map=None):
     """Checks shared by the ragged entry points.  `per_row`: tensors whose first dimension is the packed
     row count `rows`.  Returns the problem descriptor with Q = max_queries."""
     _chk(value, "value", _VAL); _chk(dist, "value_dpt_dist", _VAL)
@@ -429,7 +465,7 @@ def _ragged_common(value, dist, shapes3, lsi, query_offsets, max_queries, rows, 
     _same_device(value, dist, shapes3, lsi, query_offsets, *per_row)
     B, N, H, C = value.shape
     Bd, Nd, D, hs = _dist_problem(dist, H)
-    if (Bd, Nd) != (B, N) or query_offsets.numel() != B + 1:
+    if Bd != B or not _dist_rows_ok(Nd, N, dist_map) or query_offsets.numel() != B + 1:
         raise RuntimeError("inconsistent shapes between value, value_dpt_dist and query_offsets (B+1)")
     if int(max_queries) < 0:
         raise RuntimeError("max_queries must be >= 0")
@@ -438,7 +474,7 @@ def _ragged_common(value, dist, shapes3, lsi, query_offsets, max_queries, rows, 
 
 def dfa3d_fused_forward_ragged(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                                sampling_locations, attention_weights, query_offsets, max_queries,
-                               need_depth_score=True):
+                               need_depth_score=True, dist_map=None):
     """sampling_locations (R,H,L,P,3), attention_weights (R,H,L,P) -> (output (R,H*C), depth_score
     (R,H,L,P,4) or None)."""
     if sampling_locations.dim() != 5 or sampling_locations.shape[-1] != 3:
@@ -447,14 +483,15 @@ def dfa3d_fused_forward_ragged(value, value_dpt_dist, value_spatial_shapes, valu
     B, N, H, C, D, hs = _ragged_common(value, value_dpt_dist, value_spatial_shapes,
                                        value_level_start_index, query_offsets, max_queries, R,
                                        (sampling_locations, attention_weights),
-                                       ("sampling_loc", "attn_weight"))
+                                       ("sampling_loc", "attn_weight"), dist_map)
     if Hq != H or tuple(attention_weights.shape) != (R, H, L, P):
         raise RuntimeError("inconsistent shapes between value, sampling_loc and attn_weight")
     _level_table(value_spatial_shapes, value_level_start_index, L, 3)
     dev = value.device
     out = torch.empty((R, H * C), dtype=torch.float32, device=dev)
     ds = torch.empty((R, H, L, P, 4), dtype=torch.float32, device=dev) if need_depth_score else None
-    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(value_dpt_dist), hs)
+    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(value_dpt_dist), hs,
+                      *_map(dist_map))
     with torch.cuda.device(dev):
         _lib.call("dfa3d_fused_forward_ragged", pr, _ptr(query_offsets), _ptr(value), _ptr(value_dpt_dist),
                   _ptr(value_spatial_shapes), _ptr(value_level_start_index), _ptr(sampling_locations),
@@ -465,14 +502,14 @@ def dfa3d_fused_forward_ragged(value, value_dpt_dist, value_spatial_shapes, valu
 def dfa3d_fused_backward_ragged(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                                 sampling_locations, attention_weights, query_offsets, max_queries,
                                 grad_output, grad_value, grad_value_dpt_dist, grad_sampling_loc,
-                                grad_attn_weight):
+                                grad_attn_weight, dist_map=None):
     """Accumulates into grad_value / grad_value_dpt_dist (float32, caller-zeroed); overwrites
     grad_sampling_loc (R,H,L,P,3) and grad_attn_weight (R,H,L,P)."""
     R, Hq, L, P, _ = sampling_locations.shape
     B, N, H, C, D, hs = _ragged_common(
         value, value_dpt_dist, value_spatial_shapes, value_level_start_index, query_offsets, max_queries,
         R, (sampling_locations, attention_weights, grad_output, grad_sampling_loc, grad_attn_weight),
-        ("sampling_loc", "attn_weight", "grad_output", "grad_sampling_loc", "grad_attn_weight"))
+        ("sampling_loc", "attn_weight", "grad_output", "grad_sampling_loc", "grad_attn_weight"), dist_map)
     _chk(grad_value, "grad_value", _F32); _chk(grad_value_dpt_dist, "grad_value_dpt_dist", _F32)
     _same_device(value, grad_value, grad_value_dpt_dist)
     if Hq != H or grad_output.numel() != R * H * C or grad_value.shape != value.shape \
@@ -481,7 +518,8 @@ def dfa3d_fused_backward_ragged(value, value_dpt_dist, value_spatial_shapes, val
             or grad_attn_weight.shape != attention_weights.shape:
         raise RuntimeError("inconsistent shapes in dfa3d_fused_backward_ragged")
     _level_table(value_spatial_shapes, value_level_start_index, L, 3)
-    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(value_dpt_dist), hs)
+    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(value_dpt_dist), hs,
+                      *_map(dist_map))
     with torch.cuda.device(value.device):
         _lib.call("dfa3d_fused_backward_ragged", pr, _ptr(query_offsets), _ptr(value),
                   _ptr(value_dpt_dist), _ptr(value_spatial_shapes), _ptr(value_level_start_index),
@@ -491,7 +529,7 @@ def dfa3d_fused_backward_ragged(value, value_dpt_dist, value_spatial_shapes, val
 
 
 def _attn3d_ragged_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits, query_offsets,
-                           max_queries, extra=(), extra_names=()):
+                           max_queries, extra=(), extra_names=(), dist_map=None):
     if off_uv.dim() != 5 or off_uv.shape[-1] != 2:
         raise RuntimeError(f"sampling_offsets_uv must be (R,H,L,P,2), got {tuple(off_uv.shape)}")
     R, Hq, L, P, _ = off_uv.shape
@@ -499,7 +537,7 @@ def _attn3d_ragged_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits
         value, dist, shapes3, lsi, query_offsets, max_queries, R,
         (ref, off_uv, off_d, logits) + tuple(extra),
         ("reference_points", "sampling_offsets_uv", "sampling_offsets_depth", "attention_logits")
-        + tuple(extra_names))
+        + tuple(extra_names), dist_map)
     if ref.dim() != 3 or ref.shape[-1] != 3:
         raise RuntimeError(f"reference_points must be (R,Z,3), got {tuple(ref.shape)}")
     Z = ref.shape[1]
@@ -508,18 +546,19 @@ def _attn3d_ragged_problem(value, dist, shapes3, lsi, ref, off_uv, off_d, logits
     if Hq != H or off_d.numel() != R * H * L * P or logits.numel() != R * H * L * P:
         raise RuntimeError("inconsistent shapes between value, offsets and logits")
     _level_table(shapes3, lsi, L, 3)
-    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(dist), hs)
+    pr = _lib.Problem(B, N, H, C, D, L, int(max_queries), P, _dt(value), _dt(dist), hs, *_map(dist_map))
     return pr, Z, (R, H, C)
 
 
 def dfa3d_attn3d_forward_ragged(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                                 reference_points, sampling_offsets_uv, sampling_offsets_depth,
-                                attention_logits, query_offsets, max_queries):
+                                attention_logits, query_offsets, max_queries, dist_map=None):
     """reference_points (R,Z,3); sampling_offsets_uv (R,H,L,P,2); sampling_offsets_depth (R,H,L,P);
     attention_logits (R,H,L*P).  Returns output (R,H*C)."""
     pr, Z, (R, H, C) = _attn3d_ragged_problem(
         value, value_dpt_dist, value_spatial_shapes, value_level_start_index, reference_points,
-        sampling_offsets_uv, sampling_offsets_depth, attention_logits, query_offsets, max_queries)
+        sampling_offsets_uv, sampling_offsets_depth, attention_logits, query_offsets, max_queries,
+        dist_map=dist_map)
     out = torch.empty((R, H * C), dtype=torch.float32, device=value.device)
     with torch.cuda.device(value.device):
         _lib.call("dfa3d_attn3d_forward_ragged", pr, Z, _ptr(query_offsets), _ptr(value),
@@ -532,14 +571,15 @@ def dfa3d_attn3d_forward_ragged(value, value_dpt_dist, value_spatial_shapes, val
 def dfa3d_attn3d_backward_ragged(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                                  reference_points, sampling_offsets_uv, sampling_offsets_depth,
                                  attention_logits, query_offsets, max_queries, grad_output, grad_value,
-                                 grad_value_dpt_dist, grad_offsets_uv, grad_offsets_depth, grad_logits):
+                                 grad_value_dpt_dist, grad_offsets_uv, grad_offsets_depth, grad_logits,
+                                 dist_map=None):
     """Accumulates into grad_value / grad_value_dpt_dist (float32, caller-zeroed); overwrites the
     gradients of the offsets and of the logits (packed rows)."""
     pr, Z, (R, H, C) = _attn3d_ragged_problem(
         value, value_dpt_dist, value_spatial_shapes, value_level_start_index, reference_points,
         sampling_offsets_uv, sampling_offsets_depth, attention_logits, query_offsets, max_queries,
         (grad_output, grad_offsets_uv, grad_offsets_depth, grad_logits),
-        ("grad_output", "grad_offsets_uv", "grad_offsets_depth", "grad_logits"))
+        ("grad_output", "grad_offsets_uv", "grad_offsets_depth", "grad_logits"), dist_map)
     _chk(grad_value, "grad_value", _F32); _chk(grad_value_dpt_dist, "grad_value_dpt_dist", _F32)
     _same_device(value, grad_value, grad_value_dpt_dist)
     if grad_output.numel() != R * H * C or grad_value.shape != value.shape \

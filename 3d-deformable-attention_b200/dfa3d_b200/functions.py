@@ -79,14 +79,20 @@ class WeightedMultiScaleDeformableAttnFunction(Function):
 class MultiScale3DDeformableAttnFunction(Function):
     @staticmethod
     def forward(ctx, value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
-                sampling_locations, attention_weights, im2col_step, return_depth_score=True):
+                sampling_locations, attention_weights, im2col_step, return_depth_score=True,
+                dist_map=None):
         """value (B,N,H,C); value_dpt_dist (B,N,H,D) or (B,N,D); spatial shapes (L,3);
-        locations (B,Q,H,L,P,3); attention (B,Q,H,L,P).  Returns (output (B,Q,H*C), depth_score)."""
+        locations (B,Q,H,L,P,3); attention (B,Q,H,L,P).  Returns (output (B,Q,H*C), depth_score).
+        dist_map=(h, w): value_dpt_dist is one h x w map per camera, (B,h*w,D) or (B,h*w,H,D), that all
+        levels read with nearest indexing (the reference resizes it to every level first,
+        depth_head.py:273-276)."""
         ctx.im2col_step = im2col_step
+        ctx.dist_map = dist_map
         ctx.set_materialize_grads(False)
         output, depth_score = ext_module.dfa3d_fused_forward(
             value, value_dpt_dist, value_spatial_shapes, value_level_start_index, sampling_locations,
-            attention_weights, im2col_step=ctx.im2col_step, need_depth_score=return_depth_score)
+            attention_weights, im2col_step=ctx.im2col_step, need_depth_score=return_depth_score,
+            dist_map=dist_map)
         ctx.save_for_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                               sampling_locations, attention_weights)
         return output, depth_score
@@ -101,15 +107,15 @@ class MultiScale3DDeformableAttnFunction(Function):
             raise NotImplementedError
         value, dist, shapes, lsi, loc, attn = ctx.saved_tensors
         if grad_output is None:
-            return (None,) * 8
+            return (None,) * 9
         grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
         grad_dist = torch.zeros(dist.shape, dtype=torch.float32, device=dist.device)
         grad_sampling_loc = torch.empty_like(loc)
         grad_attn_weight = torch.empty_like(attn)
         ext_module.dfa3d_fused_backward(
             value, dist, shapes, lsi, loc, attn, grad_output.contiguous(), grad_value, grad_dist,
-            grad_sampling_loc, grad_attn_weight, im2col_step=ctx.im2col_step)
-        return grad_value, grad_dist, None, None, grad_sampling_loc, grad_attn_weight, None, None
+            grad_sampling_loc, grad_attn_weight, im2col_step=ctx.im2col_step, dist_map=ctx.dist_map)
+        return grad_value, grad_dist, None, None, grad_sampling_loc, grad_attn_weight, None, None, None
 
 
 class MultiScaleDeformableAttnFunction(Function):
@@ -154,10 +160,12 @@ class DeformableAttn3DFromOffsetsFunction(Function):
 
     @staticmethod
     def forward(ctx, value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
-                reference_points, sampling_offsets_uv, sampling_offsets_depth, attention_logits):
+                reference_points, sampling_offsets_uv, sampling_offsets_depth, attention_logits,
+                dist_map=None):
+        ctx.dist_map = dist_map
         output = ext_module.dfa3d_attn3d_forward(
             value, value_dpt_dist, value_spatial_shapes, value_level_start_index, reference_points,
-            sampling_offsets_uv, sampling_offsets_depth, attention_logits)
+            sampling_offsets_uv, sampling_offsets_depth, attention_logits, dist_map=dist_map)
         ctx.save_for_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                               reference_points, sampling_offsets_uv, sampling_offsets_depth,
                               attention_logits)
@@ -174,8 +182,8 @@ class DeformableAttn3DFromOffsetsFunction(Function):
         grad_logits = torch.empty_like(logits)
         ext_module.dfa3d_attn3d_backward(value, dist, shapes, lsi, ref, off_uv, off_d, logits,
                                          grad_output.contiguous(), grad_value, grad_dist, grad_uv, grad_d,
-                                         grad_logits)
-        return grad_value, grad_dist, None, None, None, grad_uv, grad_d, grad_logits
+                                         grad_logits, dist_map=ctx.dist_map)
+        return grad_value, grad_dist, None, None, None, grad_uv, grad_d, grad_logits, None
 
 
 class MultiScale3DDeformableAttnRaggedFunction(Function):
@@ -188,12 +196,14 @@ class MultiScale3DDeformableAttnRaggedFunction(Function):
     @staticmethod
     def forward(ctx, value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                 sampling_locations, attention_weights, query_offsets, max_queries,
-                return_depth_score=True):
+                return_depth_score=True, dist_map=None):
         ctx.max_queries = int(max_queries)
+        ctx.dist_map = dist_map
         ctx.set_materialize_grads(False)
         output, depth_score = ext_module.dfa3d_fused_forward_ragged(
             value, value_dpt_dist, value_spatial_shapes, value_level_start_index, sampling_locations,
-            attention_weights, query_offsets, ctx.max_queries, need_depth_score=return_depth_score)
+            attention_weights, query_offsets, ctx.max_queries, need_depth_score=return_depth_score,
+            dist_map=dist_map)
         ctx.save_for_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                               sampling_locations, attention_weights, query_offsets)
         return output, depth_score
@@ -205,15 +215,16 @@ class MultiScale3DDeformableAttnRaggedFunction(Function):
             raise NotImplementedError      # as the dense Function: depth_score carries no gradient
         value, dist, shapes, lsi, loc, attn, q_off = ctx.saved_tensors
         if grad_output is None:
-            return (None,) * 9
+            return (None,) * 10
         grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
         grad_dist = torch.zeros(dist.shape, dtype=torch.float32, device=dist.device)
         grad_sampling_loc = torch.empty_like(loc)
         grad_attn_weight = torch.empty_like(attn)
         ext_module.dfa3d_fused_backward_ragged(
             value, dist, shapes, lsi, loc, attn, q_off, ctx.max_queries, grad_output.contiguous(),
-            grad_value, grad_dist, grad_sampling_loc, grad_attn_weight)
-        return grad_value, grad_dist, None, None, grad_sampling_loc, grad_attn_weight, None, None, None
+            grad_value, grad_dist, grad_sampling_loc, grad_attn_weight, dist_map=ctx.dist_map)
+        return (grad_value, grad_dist, None, None, grad_sampling_loc, grad_attn_weight, None, None, None,
+                None)
 
 
 class DeformableAttn3DFromOffsetsRaggedFunction(Function):
@@ -224,11 +235,13 @@ class DeformableAttn3DFromOffsetsRaggedFunction(Function):
     @staticmethod
     def forward(ctx, value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                 reference_points, sampling_offsets_uv, sampling_offsets_depth, attention_logits,
-                query_offsets, max_queries):
+                query_offsets, max_queries, dist_map=None):
         ctx.max_queries = int(max_queries)
+        ctx.dist_map = dist_map
         output = ext_module.dfa3d_attn3d_forward_ragged(
             value, value_dpt_dist, value_spatial_shapes, value_level_start_index, reference_points,
-            sampling_offsets_uv, sampling_offsets_depth, attention_logits, query_offsets, ctx.max_queries)
+            sampling_offsets_uv, sampling_offsets_depth, attention_logits, query_offsets, ctx.max_queries,
+            dist_map=dist_map)
         ctx.save_for_backward(value, value_dpt_dist, value_spatial_shapes, value_level_start_index,
                               reference_points, sampling_offsets_uv, sampling_offsets_depth,
                               attention_logits, query_offsets)
@@ -245,8 +258,9 @@ class DeformableAttn3DFromOffsetsRaggedFunction(Function):
         grad_logits = torch.empty_like(logits)
         ext_module.dfa3d_attn3d_backward_ragged(value, dist, shapes, lsi, ref, off_uv, off_d, logits, q_off,
                                                 ctx.max_queries, grad_output.contiguous(), grad_value,
-                                                grad_dist, grad_uv, grad_d, grad_logits)
-        return grad_value, grad_dist, None, None, None, grad_uv, grad_d, grad_logits, None, None
+                                                grad_dist, grad_uv, grad_d, grad_logits,
+                                                dist_map=ctx.dist_map)
+        return grad_value, grad_dist, None, None, None, grad_uv, grad_d, grad_logits, None, None, None
 
 
 def _fp32_variant(cls, name):

@@ -125,7 +125,8 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
             nn.init.zeros_(self.value_proj.bias)
 
     def forward(self, query, value, value_dpt_dist, reference_points, spatial_shapes, level_start_index,
-                query_pos=None, key_padding_mask=None, query_offsets=None, max_queries=None):
+                query_pos=None, key_padding_mask=None, query_offsets=None, max_queries=None,
+                dist_map=None):
         """query (bs, Q, E); value (bs, N, E); value_dpt_dist (bs, N, D); reference_points
         (bs, Q, Z, 3); spatial_shapes (L, 2) int64; level_start_index (L) int64.
         Returns (output (bs, Q, E), weight_update (bs, Q, H, 1))  -- :428-583.
@@ -133,7 +134,10 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
         Packed rows (cameras with different numbers of queries): pass ``query_offsets`` (bs+1 int32,
         CUDA; element b of value owns the rows [query_offsets[b], query_offsets[b+1])) and
         ``max_queries``; then query is (R, E), reference_points (R, Z, 3), and the results are
-        (R, E) and (R, H, 1).  value / value_dpt_dist are batch-first in this mode."""
+        (R, E) and (R, H, 1).  value / value_dpt_dist are batch-first in this mode.
+
+        ``dist_map=(h, w)``: value_dpt_dist is one h x w map per camera, (bs, h*w, D), that every level
+        reads with nearest-neighbour indexing (instead of one resized copy per level)."""
         ragged = query_offsets is not None
         if query_pos is not None:
             query = query + query_pos
@@ -158,11 +162,12 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
             if ragged:
                 output = DeformableAttn3DFromOffsetsRaggedFunction_fp32.apply(
                     value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
-                    reference_points.contiguous(), off_uv, off_d, logits, query_offsets, max_queries)
+                    reference_points.contiguous(), off_uv, off_d, logits, query_offsets, max_queries,
+                    dist_map)
                 return output, None
             output = DeformableAttn3DFromOffsetsFunction_fp32.apply(
                 value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
-                reference_points.contiguous(), off_uv, off_d, logits)
+                reference_points.contiguous(), off_uv, off_d, logits, dist_map)
             return (output if self.batch_first else output.permute(1, 0, 2)), None
         attn = logits.softmax(-1).view(*lead, H, L, P)
         if ragged:
@@ -170,12 +175,13 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
                                               spatial_shapes, D)[0]
             output, depth_score = MultiScale3DDeformableAttnRaggedFunction_fp32.apply(
                 value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
-                loc.contiguous(), attn.contiguous(), query_offsets, max_queries, self.compute_weight_update)
+                loc.contiguous(), attn.contiguous(), query_offsets, max_queries, self.compute_weight_update,
+                dist_map)
         else:
             loc = assemble_sampling_locations(reference_points, off_uv, off_d, spatial_shapes, D)
             output, depth_score = MultiScale3DDeformableAttnFunction_fp32.apply(
                 value.contiguous(), value_dpt_dist.contiguous(), shapes3, level_start_index,
-                loc.contiguous(), attn.contiguous(), self.im2col_step, self.compute_weight_update)
+                loc.contiguous(), attn.contiguous(), self.im2col_step, self.compute_weight_update, dist_map)
         weight_update = None
         if self.compute_weight_update:
             # mean depth score of a point's four corners, weighted by the attention (:579)
@@ -205,13 +211,14 @@ class SpatialCrossAttention_DFA3D(nn.Module):
 
     def forward(self, query, key=None, value=None, value_dpt_dist=None, reference_points_cam=None,
                 bev_mask=None, spatial_shapes=None, level_start_index=None, residual=None,
-                query_pos=None, rebatch_plan=None):
+                query_pos=None, rebatch_plan=None, dist_map=None):
         """query (bs, Q, E); value (num_cams, N, bs, E) (`key` is accepted and, as in the reference,
         not used by the attention); value_dpt_dist (num_cams, N, bs, D);
         reference_points_cam (num_cams, bs, Q, Z, 3); bev_mask (num_cams, bs, Q, Z).
         ``rebatch_plan``: a ``RebatchPlan`` of this bev_mask built earlier (bev_mask is geometry: one
         plan serves every layer of a frame); without it the plan is built here, which reads the packed
-        row count back from the device once.  Returns (bs, Q, E)."""
+        row count back from the device once.  ``dist_map=(h, w)``: value_dpt_dist is one h x w map per
+        camera, (num_cams, h*w, bs, D), read by all levels with nearest indexing.  Returns (bs, Q, E)."""
         inp_residual = query if residual is None else residual
         if query_pos is not None:
             query = query + query_pos
@@ -228,7 +235,7 @@ class SpatialCrossAttention_DFA3D(nn.Module):
         out_rows, update_weight = self.deformable_attention(
             query=q_rows, value=value, value_dpt_dist=dist, reference_points=ref_rows,
             spatial_shapes=spatial_shapes, level_start_index=level_start_index,
-            query_offsets=plan.op_offsets, max_queries=plan.max_queries)
+            query_offsets=plan.op_offsets, max_queries=plan.max_queries, dist_map=dist_map)
         if self.use_empty:
             # :721-722, :739-740 -- rows whose depth-weighted attention found little get the learned
             # per-(BEV cell, head) empty embedding instead

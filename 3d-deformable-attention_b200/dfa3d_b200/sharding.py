@@ -60,6 +60,28 @@ def shard_queries(num_queries, world_size, rank):
     return slice(r.start, r.stop)
 
 
+def camera_query_grid(num_cameras, world_size, rank, camera_groups=0):
+    """Two-dimensional split of ONE batch of camera frames over the ranks: `camera_groups` groups of
+    ranks, each owning a contiguous block of cameras; inside a group the queries are split.  Gradients
+    with respect to value / dist are then partial sums only over the ranks of one group, so the
+    exchange moves 1/camera_groups of the bytes among world_size/camera_groups ranks.
+
+    camera_groups = 0 picks the largest number of groups that divides both world_size and the number
+    of cameras, so that every rank gets the same work (more groups = less to exchange; with world_size
+    groups nothing at all).
+    Returns (group index, ranks of this rank's group, camera slice, query block index, query blocks)."""
+    g = int(camera_groups)
+    if g <= 0:
+        g = max(d for d in range(1, world_size + 1) if world_size % d == 0 and num_cameras % d == 0)
+    if world_size % g != 0 or g > num_cameras:
+        raise ValueError(f"camera_groups={g} must divide world_size={world_size} and not exceed "
+                         f"the {num_cameras} cameras")
+    per = world_size // g
+    gi, qi = rank // per, rank % per
+    cams = shard_frames(num_cameras, g, gi)
+    return gi, list(range(gi * per, (gi + 1) * per)), slice(cams.start, cams.stop), qi, per
+
+
 def allreduce_sum_(tensors, group=None, async_op=False):
     """In-place SUM all-reduce of each tensor over the group (the exchange step of the query-block
     mode: grad_value and grad_dist are partial sums over the ranks' query blocks).  Returns the list of

@@ -319,45 +319,66 @@ def run_encoder_stack(a, rank, world, local):
         dist_.destroy_process_group()
 
 
-def run_query_blocks(a, w, rank, world, local):
-    """--scaling strong: ONE batch of camera frames, its queries split over the ranks (query-block
-    mode).  value / dist are replicated by one NCCL broadcast (outside the timed region: they are the
-    layer's inputs, resident before the op runs); a step is fused forward + backward on the rank's
-    query block, one group of cameras at a time, with the SUM all-reduce of the group's grad_value /
-    grad_dist (partial sums over query blocks) issued asynchronously while the next group computes."""
+def measure_query_blocks(a, w, rank, world, dev, steps, warmup):
+    """Query-block mode: ONE batch of camera frames on all ranks.  The ranks form camera groups; inside
+    a group the queries are split (dfa3d_b200.sharding.camera_query_grid).  value / dist are replicated
+    by one NCCL broadcast (outside the timed region: they are the layer's inputs, resident before the op
+    runs); a step is fused forward + backward on the rank's query block, one sub-group of cameras at a
+    time, with the exchange of that sub-group's grad_value / grad_dist (partial sums over the group's
+    query blocks) issued asynchronously while the next sub-group computes.  The exchange is an
+    all-reduce (every rank of the group ends with the full gradient) or a reduce-scatter (every rank
+    ends with its 1/group share of it).  Returns the result dict (identical on every rank)."""
     from dfa3d_b200 import ext, sharding, workloads as wl
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist_.init_process_group("nccl", device_id=dev)
-    d = wl.make_inputs(w)                                    # same seed on every rank: same frame
-    qs = sharding.shard_queries(w.Q, world, rank)
+    gi, ranks, cams, qi, qblocks = sharding.camera_query_grid(w.B, world, rank, a.camera_groups)
+    ngroups = world // qblocks
+    group = None
+    if world > 1 and qblocks > 1:
+        for g in range(ngroups):                                 # every rank creates every group
+            pg = dist_.new_group(list(range(g * qblocks, (g + 1) * qblocks)))
+            if g == gi:
+                group = pg
+    d = wl.make_inputs(w)                                        # same seed on every rank: same batch
+    qs = sharding.shard_queries(w.Q, qblocks, qi)
     value = d["value"].to(dev) if rank == 0 else torch.empty_like(d["value"], device=dev)
     dist = d["dist"].to(dev) if rank == 0 else torch.empty_like(d["dist"], device=dev)
     if world > 1:
         dist_.broadcast(value, 0)
         dist_.broadcast(dist, 0)
-    loc = d["loc"][:, qs].contiguous().to(dev)
-    attn = d["attn"][:, qs].contiguous().to(dev)
-    go = d["grad_out"][:, qs].contiguous().to(dev)
+    value, dist = value[cams].contiguous(), dist[cams].contiguous()
+    loc = d["loc"][cams, qs].contiguous().to(dev)
+    attn = d["attn"][cams, qs].contiguous().to(dev)
+    go = d["grad_out"][cams, qs].contiguous().to(dev)
     shapes, lsi = d["shapes"].to(dev), d["lsi"].to(dev)
+    ncam = value.shape[0]
     gv = torch.zeros_like(value); gd = torch.zeros_like(dist)
     gl = torch.empty_like(loc); ga = torch.empty_like(attn)
-    out = torch.empty(w.B, loc.shape[1], w.H * w.C, device=dev)
-
-    groups = max(1, min(a.exchange_groups, w.B))            # cameras are exchanged in this many groups
-    bounds = [round(i * w.B / groups) for i in range(groups + 1)]
+    out = torch.empty(ncam, loc.shape[1], w.H * w.C, device=dev)
+    sub = max(1, min(a.exchange_groups, ncam))                   # cameras are exchanged in this many parts
+    bounds = [round(i * ncam / sub) for i in range(sub + 1)]
+    scatter = a.exchange == "reduce_scatter" and qblocks > 1
+    shards = []
+    if scatter:                                                  # this rank's share of each part's gradient
+        for g0, g1 in zip(bounds[:-1], bounds[1:]):
+            n = gv[g0:g1].numel() + gd[g0:g1].numel()
+            shards.append((torch.empty((n + qblocks - 1) // qblocks * qblocks, device=dev),
+                           torch.empty((n + qblocks - 1) // qblocks, device=dev)))
 
     def step():
         works = []
-        for g0, g1 in zip(bounds[:-1], bounds[1:]):
+        for i, (g0, g1) in enumerate(zip(bounds[:-1], bounds[1:])):
             sl = slice(g0, g1)
             ext.dfa3d_fused_forward(value[sl], dist[sl], shapes, lsi, loc[sl], attn[sl], 64,
                                     need_depth_score=False, out=out[sl])
             gv[sl].zero_(); gd[sl].zero_()
             ext.dfa3d_fused_backward(value[sl], dist[sl], shapes, lsi, loc[sl], attn[sl], go[sl], gv[sl],
                                      gd[sl], gl[sl], ga[sl], 64)
-            works += sharding.allreduce_sum_([gv[sl], gd[sl]], async_op=True)
+            if scatter:
+                flat, mine = shards[i]
+                nv = gv[sl].numel()
+                flat[:nv].copy_(gv[sl].reshape(-1)); flat[nv:nv + gd[sl].numel()].copy_(gd[sl].reshape(-1))
+                works.append(dist_.reduce_scatter_tensor(mine, flat, group=group, async_op=True))
+            elif qblocks > 1:
+                works += sharding.allreduce_sum_([gv[sl], gd[sl]], group=group, async_op=True)
         for wk in works:
             wk.wait()
 
@@ -366,38 +387,68 @@ def run_query_blocks(a, w, rank, world, local):
             dist_.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(a.warmup):
+    for _ in range(warmup):
         step()
     barrier()
-    sampler = ClockSampler(local)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
     e0.record()
-    for _ in range(a.steps):
+    for _ in range(steps):
         step()
     e1.record()
     barrier()
-    clocks = sampler.stop()
-    ms = sharding.max_over_ranks(e0.elapsed_time(e1), device=dev) / a.steps
-    # parity of the exchange: the all-reduced gradient must satisfy the same adjoint identity as on one GPU
-    lhs = torch.tensor([(go.double() * out.double()).sum().item()], device=dev, dtype=torch.float64)
+    ms = sharding.max_over_ranks(e0.elapsed_time(e1), device=dev) / steps
+    # parity of the exchange: the exchanged gradient must satisfy the same adjoint identity as on one
+    # GPU, <grad_out, out> summed over all ranks == <grad_value, value> summed over the camera groups
+    lhs = (go.double() * out.double()).sum()
+    if scatter:
+        rhs = torch.zeros((), dtype=torch.float64, device=dev)
+        for i, (g0, g1) in enumerate(zip(bounds[:-1], bounds[1:])):
+            flat, mine = shards[i]
+            n = mine.numel()
+            vflat = torch.cat([value[g0:g1].reshape(-1), torch.zeros_like(gd[g0:g1]).reshape(-1)])
+            vflat = torch.nn.functional.pad(vflat, (0, flat.numel() - vflat.numel()))
+            rhs += (mine.double() * vflat[qi * n:(qi + 1) * n].double()).sum()
+    else:
+        rhs = (gv.double() * value.double()).sum() / qblocks      # every rank of the group holds the full sum
+    both = torch.stack([lhs, rhs])
     if world > 1:
-        dist_.all_reduce(lhs)
-    rhs = (gv.double() * value.double()).sum().item()
-    assert abs(lhs.item() - rhs) <= 1e-4 * abs(rhs), (lhs.item(), rhs)
+        dist_.all_reduce(both)
+    lhs, rhs = both.tolist()
+    assert abs(lhs - rhs) <= 1e-4 * abs(rhs), (lhs, rhs)
+    exchanged = (gv.numel() + gd.numel()) * 4 if qblocks > 1 else 0
+    return {"value": w.points / (ms * 1e-3), "unit": "sampled points/s", "ms_per_step": ms,
+            "n_gpus": world, "steps": steps, "scaling": "strong",
+            "mode": "query blocks: %d camera group(s) x %d query block(s); value/dist broadcast once; "
+                    "grad_value/grad_dist exchanged inside a camera group by NCCL %s, in %d part(s) "
+                    "overlapped with the kernels" % (ngroups, qblocks, a.exchange if qblocks > 1 else "(nothing)",
+                                                     sub),
+            "camera_groups": ngroups, "query_blocks": qblocks, "cameras_per_rank": ncam,
+            "queries_per_rank": loc.shape[1], "points_total": w.points,
+            "exchange_bytes_per_rank_step": exchanged, "gpu_launches": 2 * sub * steps}
+
+
+def run_query_blocks(a, w, rank, world, local):
+    """--scaling strong: the query-block mode as the bench's only measurement."""
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist_.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local)
+    sampler.start()
+    r = measure_query_blocks(a, w, rank, world, dev, a.steps, a.warmup)
+    clocks = sampler.stop()
     if rank == 0:
-        fwd_b, bwd_b = w.algorithmic_bytes()
         print(json.dumps({
-            "metric": "DFA3D fwd+bwd sampled points/s", "value": w.points / (ms * 1e-3),
-            "unit": "sampled points/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": w.name, "mode": "query blocks: Q split over ranks, value/dist "
-                       "broadcast once, grad_value/grad_dist all-reduced per camera group (NCCL, overlapped)",
-                       "exchange_groups": groups,
-                       "cameras": w.B, "queries_per_rank": loc.shape[1], "points_total": w.points,
-                       "allreduce_bytes_per_step": (gv.numel() + gd.numel()) * 4},
-            "clocks": clocks, "gpu_launches": 2 * groups * a.steps}), flush=True)
+            "metric": "DFA3D fwd+bwd sampled points/s", "value": r["value"], "unit": r["unit"],
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": w.name, "mode": r["mode"], "camera_groups": r["camera_groups"],
+                       "query_blocks": r["query_blocks"], "cameras": w.B,
+                       "cameras_per_rank": r["cameras_per_rank"], "queries_per_rank": r["queries_per_rank"],
+                       "points_total": w.points,
+                       "exchange_bytes_per_rank_step": r["exchange_bytes_per_rank_step"]},
+            "clocks": clocks, "gpu_launches": r["gpu_launches"]}), flush=True)
     if world > 1:
         dist_.destroy_process_group()
 
@@ -419,6 +470,11 @@ def main():
     ap.add_argument("--exchange-groups", type=int, default=3,
                     help="strong scaling: number of camera groups whose gradient all-reduce overlaps "
                          "the next group's kernels")
+    ap.add_argument("--camera-groups", type=int, default=0,
+                    help="strong scaling: number of camera groups (0 = the largest that divides both "
+                         "the GPUs and the cameras); queries are split inside a group")
+    ap.add_argument("--exchange", choices=("all_reduce", "reduce_scatter"), default="all_reduce",
+                    help="strong scaling: how a camera group combines its partial grad_value/grad_dist")
     ap.add_argument("--cameras", type=int, default=0,
                     help="override the workload's cameras per GPU (small cases for profiler captures)")
     a = ap.parse_args()
@@ -537,6 +593,9 @@ def main():
         extra["function_level"] = ("MultiScale3DDeformableAttnFunction_fp32.apply + backward, "
                                    "allocations and depth_score output included")
         extra.update(measure_extras(a, w, dev, world, rank, barrier))
+        if world > 1 and w.name == "cfg2":
+            # the other way to use several GPUs: one batch, split by cameras and queries (strong scaling)
+            extra["query_blocks"] = measure_query_blocks(a, w, rank, world, dev, max(10, min(a.steps, 50)), 3)
         if rank == 0 and w.L * w.P == 32 and w.H == 8 and w.C == 32 and w.value_dtype == "fp32":
             extra["memory_stream_floor"] = memory_stream_floor(w)
 

@@ -37,6 +37,9 @@ extern "C" {
 #define DFA3D_DTYPE_F32 0
 #define DFA3D_DTYPE_BF16 1
 
+#define DFA3D_ACT_SOFTMAX 0 /* dfa3d_dist_from_logits: softmax over the D channels */
+#define DFA3D_ACT_SIGMOID 1 /* element-wise sigmoid */
+
 #define DFA3D_MAX_LEVELS 32   /* L */
 #define DFA3D_MAX_CHANNELS 1024 /* C; reference kernels for C > 1024 are themselves broken
                                    (wms_deform_attn_cuda_kernel.cuh:968-971 pass un-offset pointers) */
@@ -232,6 +235,29 @@ int dfa3d_rebatch_gather(const float *src, const int32_t *packed_query, const in
 int dfa3d_rebatch_combine(const float *src, const int32_t *row_of, const int32_t *offsets, int32_t cams,
                           int32_t bs, int32_t Q, int32_t width, const float *scale, float *dst,
                           void *stream);
+
+/* Producer of `dist`: the depth network's logits (B, D, map_h, map_w) fp32 become the operator's
+ * dist (B, N, D), fp32 or bf16, in one pass: softmax over D (or sigmoid), nearest-neighbour resize to
+ * every level (spatial_shapes (L, shape_stride) / level_start (L), int64, device), channel-last layout.
+ * Replaces BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/dense_heads/depth_head.py:265-276
+ * (feat_dpt.softmax(1) | sigmoid(); F.interpolate(dpt_dist, size=scale, mode="nearest") per level) and
+ * the flatten / permute / cat of …/modules/transformer.py:368-391 with the permute of
+ * spatial_cross_attention.py:727-728.  With L = 1 and the level equal to the map it writes the single
+ * map that dfa3d_problem.dist_map_h/w describe.  D <= 256.  Writes every element of dist. */
+int dfa3d_dist_from_logits(const float *logits, int32_t B, int32_t D, int32_t map_h, int32_t map_w,
+                           const int64_t *spatial_shapes, int32_t shape_stride,
+                           const int64_t *level_start, int32_t L, int32_t N, int32_t activation,
+                           int32_t dist_dtype, void *dist, void *stream);
+
+/* Its backward: grad_dist (B, N, D) fp32 -> grad_logits (B, D, map_h, map_w) fp32, i.e. autograd of the
+ * interpolate calls (sum over the level pixels that read a map pixel) chained with the softmax /
+ * sigmoid backward; the normalised bins are recomputed from the logits.  Writes every element of
+ * grad_logits. */
+int dfa3d_dist_from_logits_backward(const float *logits, int32_t B, int32_t D, int32_t map_h,
+                                    int32_t map_w, const int64_t *spatial_shapes, int32_t shape_stride,
+                                    const int64_t *level_start, int32_t L, int32_t N,
+                                    int32_t activation, const float *grad_dist, float *grad_logits,
+                                    void *stream);
 
 #ifdef __cplusplus
 }

@@ -26,7 +26,12 @@ REF_OUT = os.path.join(HERE, "_ref")
 
 
 def reference_root():
-    return os.environ.get("DFA3D_REFERENCE_ROOT", "/root/reference")
+    """Where the reference checkout lies: $DFA3D_REFERENCE_ROOT, else a directory named ``reference``
+    beside this repository."""
+    env = os.environ.get("DFA3D_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def is_built():
@@ -42,7 +47,8 @@ def build(verbose=False):
     root = reference_root()
     csrc = os.path.join(root, "DFA3D", "dfa3D", "ops", "csrc")
     if not os.path.isdir(csrc):
-        raise FileNotFoundError(f"reference checkout not found at {root}")
+        raise FileNotFoundError(f"reference checkout not found at {root}: set DFA3D_REFERENCE_ROOT to the "
+                                "directory that holds DFA3D/ and BEVFormer_DFA3D/")
     import glob
     from torch.utils import cpp_extension
 

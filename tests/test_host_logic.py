@@ -184,3 +184,24 @@ def test_world_size_2_gloo_query_block_exchange():
     for r in res:                                   # every rank ends with the full sum 0+...+6
         torch.testing.assert_close(r[2], torch.full((3,), 21.0))
     assert sharding.allreduce_sum_([torch.ones(1)]) == []      # no process group: nothing to do
+
+
+def test_camera_query_grid_covers_every_camera_query_pair_once():
+    """The 2-D split of the query-block mode: camera groups x query blocks tile the batch exactly."""
+    for cams, world in ((6, 1), (6, 2), (6, 4), (6, 8), (6, 3), (6, 6), (5, 4), (8, 8)):
+        Q = 103
+        seen = torch.zeros(cams, Q, dtype=torch.int32)
+        sizes = set()
+        for rank in range(world):
+            gi, ranks, cs, qi, qblocks = sharding.camera_query_grid(cams, world, rank)
+            assert rank in ranks and len(ranks) == qblocks and world % qblocks == 0
+            qs = sharding.shard_queries(Q, qblocks, qi)
+            seen[cs, qs] += 1
+            sizes.add(cs.stop - cs.start)
+        assert (seen == 1).all(), (cams, world)
+        assert len(sizes) == 1                      # balanced: every group owns the same number of cameras
+    # 8 GPUs, 6 cameras: 2 groups of 3 cameras x 4 query blocks; 2 GPUs: one camera group each, no exchange
+    assert sharding.camera_query_grid(6, 8, 5)[:2] == (1, [4, 5, 6, 7])
+    assert sharding.camera_query_grid(6, 2, 1)[3:] == (0, 1)
+    with pytest.raises(ValueError):
+        sharding.camera_query_grid(6, 8, 0, camera_groups=3)
