@@ -302,7 +302,7 @@ dfa3d_backward_kernel(const KArgs a) {
 #pragma unroll 1
   for (int it = 0; it < DFA3D_BWD_ITEMS_PER_WARP; ++it) {
     ItemCtx c;
-    if (!item_context(a, warp, blockIdx.x * DFA3D_BWD_ITEMS_PER_WARP + it, c)) return;
+    if (!item_context<DFA3D_BWD_HEAD_MAJOR != 0>(a, warp, blockIdx.x * DFA3D_BWD_ITEMS_PER_WARP + it, c)) return;
     backward_item<VT, DT, C, MODE, FULL>(a, lv, c, rows[warp], dots[warp], lane);
   }
 }

@@ -49,6 +49,17 @@ constexpr int kThreads = kWarpsPerCta * 32;
 #ifndef DFA3D_BWD_MIN_CTAS
 #define DFA3D_BWD_MIN_CTAS 4
 #endif
+//   *_HEAD_MAJOR      1: the items of a camera are walked head by head (all queries of head 0, then
+//                     head 1, ...) instead of query by query, so that the CTAs resident at one time
+//                     gather from, and reduce into, one or two heads' slices.  Measured: backward
+//                     -1.8 %, forward +1 % (+4 % when neighbouring queries look at neighbouring pixels,
+//                     because the eight heads of a query then share their depth-distribution lines)
+#ifndef DFA3D_FWD_HEAD_MAJOR
+#define DFA3D_FWD_HEAD_MAJOR 0
+#endif
+#ifndef DFA3D_BWD_HEAD_MAJOR
+#define DFA3D_BWD_HEAD_MAJOR 1
+#endif
 
 // Kernel argument block (device pointers + sizes).  Unused pointers are null.
 struct KArgs {
@@ -127,20 +138,35 @@ struct ItemCtx {
 // blockIdx.y (+ b0) selects the camera; the CTA's `group`-th group of kWarpsPerCta items starts at
 // (blockIdx.x * groups_per_cta + group) * kWarpsPerCta, warp w takes item w of it: a (query, head)
 // pair of that camera.  Returns false for the warps past the end of the camera.
+template <bool HEAD_MAJOR = false>
 __device__ __forceinline__ bool item_context(const KArgs &a, int warp, unsigned group, ItemCtx &c) {
   const unsigned idx = group * kWarpsPerCta + warp;
   if (idx >= (unsigned)a.items_per_cam) return false;
   c.b = (int)blockIdx.y + a.b0;
-  const unsigned q = idx / (unsigned)a.H;
-  c.h = (int)(idx - q * (unsigned)a.H);
-  if (a.q_off) {
-    const int q0 = __ldg(a.q_off + c.b);
-    if ((int)q >= __ldg(a.q_off + c.b + 1) - q0) return false;
-    c.bq = (long long)q0 + q;
+  if (HEAD_MAJOR) {
+    if (a.q_off) {
+      const int q0 = __ldg(a.q_off + c.b);
+      const unsigned nq = (unsigned)(__ldg(a.q_off + c.b + 1) - q0);
+      if (idx >= nq * (unsigned)a.H) return false;
+      c.h = (int)(idx / nq);
+      c.bq = (long long)q0 + (idx - (unsigned)c.h * nq);
+    } else {
+      c.h = (int)(idx / (unsigned)a.Q);
+      c.bq = (long long)c.b * a.Q + (idx - (unsigned)c.h * (unsigned)a.Q);
+    }
     c.item = c.bq * a.H + c.h;
   } else {
-    c.bq = (long long)c.b * a.Q + q;
-    c.item = (long long)c.b * a.items_per_cam + idx;
+    const unsigned q = idx / (unsigned)a.H;
+    c.h = (int)(idx - q * (unsigned)a.H);
+    if (a.q_off) {
+      const int q0 = __ldg(a.q_off + c.b);
+      if ((int)q >= __ldg(a.q_off + c.b + 1) - q0) return false;
+      c.bq = (long long)q0 + q;
+      c.item = c.bq * a.H + c.h;
+    } else {
+      c.bq = (long long)c.b * a.Q + q;
+      c.item = (long long)c.b * a.items_per_cam + idx;
+    }
   }
   c.pt0 = c.item * a.LP;
   c.loc = a.loc + c.pt0 * a.loc_stride;      // (not dereferenced in caller-fused mode)

@@ -161,7 +161,7 @@ dfa3d_forward_kernel(const KArgs a) {
 #pragma unroll 1
   for (int it = 0; it < DFA3D_FWD_ITEMS_PER_WARP; ++it) {
     ItemCtx c;
-    if (!item_context(a, warp, blockIdx.x * DFA3D_FWD_ITEMS_PER_WARP + it, c)) return;
+    if (!item_context<DFA3D_FWD_HEAD_MAJOR != 0>(a, warp, blockIdx.x * DFA3D_FWD_ITEMS_PER_WARP + it, c)) return;
     forward_item<VT, DT, C, MODE, WRITE_DS, FULL>(a, lv, c, rows[warp], lane);
   }
 }

@@ -32,7 +32,8 @@ class _GridSampleOp:
     """Stand-in with the dense Function's call signature, built from differentiable torch ops."""
 
     @staticmethod
-    def apply(value, dist, shapes3, lsi, loc, attn, im2col_step, return_depth_score=True):
+    def apply(value, dist, shapes3, lsi, loc, attn, im2col_step, return_depth_score=True, dist_map=None):
+        assert dist_map is None
         H = value.shape[2]
         dist_h = dist[:, :, None, :].expand(-1, -1, H, -1)
         out = G.dfa3d_grid_sample(value.double(), dist_h.double(), shapes3.tolist(), lsi.tolist(),
@@ -45,7 +46,9 @@ class _GridSampleRaggedOp:
     """Stand-in with the ragged Function's call signature: camera by camera through grid_sample."""
 
     @staticmethod
-    def apply(value, dist, shapes3, lsi, loc, attn, query_offsets, max_queries, return_depth_score=True):
+    def apply(value, dist, shapes3, lsi, loc, attn, query_offsets, max_queries, return_depth_score=True,
+              dist_map=None):
+        assert dist_map is None
         offs = query_offsets.tolist()
         outs, dss = [], []
         for b in range(value.shape[0]):
