@@ -39,8 +39,8 @@ import torch.distributed as dist_  # noqa: E402
 # kernels on 2 of the 6 cameras, times 3: cameras are independent and traffic grows in proportion).
 # Keyed by workload; a workload without a capture reports null.
 NCU_DRAM_TRAFFIC = {
-    "cfg2": {"forward": 3 * (164.163584e6 + 18.407680e6), "backward": 3 * (409.077760e6 + 212.663808e6)},
-    "cfg3": {"forward": 3 * (121.428480e6 + 14.806016e6), "backward": 3 * (242.028032e6 + 142.101504e6)},
+    "cfg2": {"forward": 3 * (191.835392e6 + 17.074688e6), "backward": 3 * (262.928384e6 + 124.026624e6)},
+    "cfg3": {"forward": 3 * (121.627904e6 + 14.459392e6), "backward": 3 * (220.926208e6 + 116.512768e6)},
 }
 
 
