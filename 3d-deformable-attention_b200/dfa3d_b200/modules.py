@@ -7,6 +7,8 @@
     BEVFormer encoder layer (…/modules/encoder.py:249-413 with the 'cross_attn', 'norm', 'ffn',
     'norm' operation order), used for the training-step configuration.
 
+  * ``TemporalSelfAttention`` -- the BEV self-attention over the previous and the current BEV
+    (…/modules/temporal_self_attention.py:26-272), the caller of the plain 2-D operator.
   * ``point_sampling`` -- the projection of the pillar reference points into the cameras that yields
     ``reference_points_cam`` and ``bev_mask`` (…/modules/encoder.py:421-476).
 
@@ -22,12 +24,37 @@ import math
 import torch
 import torch.nn as nn
 
-from .functions import (DeformableAttn3DFromOffsetsFunction_fp32,
+from .functions import (MultiScaleDeformableAttnFunction_fp32,
+                        DeformableAttn3DFromOffsetsFunction_fp32,
                         DeformableAttn3DFromOffsetsRaggedFunction_fp32,
                         MultiScale3DDeformableAttnFunction_fp32,
                         MultiScale3DDeformableAttnRaggedFunction_fp32)
 from .rebatch import (CombineCamerasFunction, GatherQueriesFunction, GatherSharedRowsFunction, RebatchPlan,
                       gather_per_camera)
+
+
+def bev_reference_points(bev_h, bev_w, pillar_height=8, num_points_in_pillar=4, dim="3d", bs=1,
+                         device="cuda", dtype=torch.float32):
+    """Reference points of the BEV queries (encoder.py:61-99).  dim="3d": (bs, num_points_in_pillar,
+    bev_h*bev_w, 3) = (x, y, z) in [0,1]^3, the pillar anchors that `point_sampling` projects into the
+    cameras; dim="2d": (bs, bev_h*bev_w, 1, 2), the cell centres the temporal self-attention looks
+    around."""
+    if dim == "3d":
+        Z, n = pillar_height, num_points_in_pillar
+        zs = torch.linspace(0.5, Z - 0.5, n, dtype=dtype, device=device).view(-1, 1, 1).expand(n, bev_h, bev_w) / Z
+        xs = torch.linspace(0.5, bev_w - 0.5, bev_w, dtype=dtype, device=device).view(1, 1, bev_w) \
+            .expand(n, bev_h, bev_w) / bev_w
+        ys = torch.linspace(0.5, bev_h - 0.5, bev_h, dtype=dtype, device=device).view(1, bev_h, 1) \
+            .expand(n, bev_h, bev_w) / bev_h
+        ref = torch.stack((xs, ys, zs), -1).permute(0, 3, 1, 2).flatten(2).permute(0, 2, 1)
+        return ref[None].repeat(bs, 1, 1, 1)
+    if dim == "2d":
+        ref_y, ref_x = torch.meshgrid(torch.linspace(0.5, bev_h - 0.5, bev_h, dtype=dtype, device=device),
+                                      torch.linspace(0.5, bev_w - 0.5, bev_w, dtype=dtype, device=device),
+                                      indexing="ij")
+        ref = torch.stack((ref_x.reshape(-1)[None] / bev_w, ref_y.reshape(-1)[None] / bev_h), -1)
+        return ref.repeat(bs, 1, 1).unsqueeze(2)
+    raise ValueError("dim must be '3d' or '2d'")
 
 
 def point_sampling(reference_points, pc_range, lidar2img, img_shape, d_bound):
@@ -247,6 +274,96 @@ class SpatialCrossAttention_DFA3D(nn.Module):
         return self.dropout(slots) + inp_residual
 
 
+class TemporalSelfAttention(nn.Module):
+    """BEV queries attend to the previous and the current BEV with 2-D multi-scale deformable attention
+    (temporal_self_attention.py:26-272; parameters and initialisation :103-127).  The operator is the
+    plain 2-D one, here on the depth-weighted kernels with all depth scores 1
+    (``MultiScaleDeformableAttnFunction_fp32``); the reference takes it from the mmcv extension."""
+
+    def __init__(self, embed_dims=256, num_heads=8, num_levels=4, num_points=4, num_bev_queue=2,
+                 im2col_step=64, dropout=0.1, batch_first=True):
+        super().__init__()
+        if embed_dims % num_heads != 0:
+            raise ValueError(f"embed_dims must be divisible by num_heads, but got {embed_dims} and "
+                             f"{num_heads}")
+        self.embed_dims, self.num_heads = embed_dims, num_heads
+        self.num_levels, self.num_points, self.num_bev_queue = num_levels, num_points, num_bev_queue
+        self.im2col_step, self.batch_first = im2col_step, batch_first
+        self.dropout = nn.Dropout(dropout)
+        self.sampling_offsets = nn.Linear(embed_dims * num_bev_queue,
+                                          num_bev_queue * num_heads * num_levels * num_points * 2)
+        self.attention_weights = nn.Linear(embed_dims * num_bev_queue,
+                                           num_bev_queue * num_heads * num_levels * num_points)
+        self.value_proj = nn.Linear(embed_dims, embed_dims)
+        self.output_proj = nn.Linear(embed_dims, embed_dims)
+        self.init_weights()
+
+    def init_weights(self):
+        H, LQ, P = self.num_heads, self.num_levels * self.num_bev_queue, self.num_points
+        nn.init.zeros_(self.sampling_offsets.weight)
+        thetas = torch.arange(H, dtype=torch.float32) * (2.0 * math.pi / H)
+        grid = torch.stack([thetas.cos(), thetas.sin()], -1)
+        grid = (grid / grid.abs().max(-1, keepdim=True)[0]).view(H, 1, 1, 2).repeat(1, LQ, P, 1)
+        grid = grid * torch.arange(1, P + 1, dtype=torch.float32).view(1, 1, P, 1)
+        with torch.no_grad():
+            self.sampling_offsets.bias.copy_(grid.view(-1))
+            nn.init.zeros_(self.attention_weights.weight)
+            nn.init.zeros_(self.attention_weights.bias)
+            nn.init.xavier_uniform_(self.value_proj.weight)
+            nn.init.zeros_(self.value_proj.bias)
+            nn.init.xavier_uniform_(self.output_proj.weight)
+            nn.init.zeros_(self.output_proj.bias)
+
+    def forward(self, query, key=None, value=None, identity=None, query_pos=None, key_padding_mask=None,
+                reference_points=None, spatial_shapes=None, level_start_index=None):
+        """query (bs, Q, E); value (bs*num_bev_queue, Q, E) = [previous BEV, current BEV] per batch
+        element, or None (then the current queries stand for both, :180-184); reference_points
+        (bs*num_bev_queue, Q, num_levels, 2); spatial_shapes (L, 2); level_start_index (L).
+        Returns (bs, Q, E)  -- :130-272."""
+        if self.num_bev_queue != 2:
+            raise ValueError("the BEV queue holds the previous and the current BEV: num_bev_queue == 2")
+        if value is None:
+            if not self.batch_first:
+                raise ValueError("value=None needs batch_first=True")
+            bs, len_bev, c = query.shape
+            value = torch.stack([query, query], 1).reshape(bs * 2, len_bev, c)
+        if identity is None:
+            identity = query
+        if query_pos is not None:
+            query = query + query_pos
+        if not self.batch_first:
+            query, value = query.permute(1, 0, 2), value.permute(1, 0, 2)
+        bs, Q, E = query.shape
+        N = value.shape[1]
+        H, L, P, NQ = self.num_heads, self.num_levels, self.num_points, self.num_bev_queue
+        query = torch.cat([value[:bs], query], -1)                        # :197
+        value = self.value_proj(value)
+        if key_padding_mask is not None:
+            value = value.masked_fill(key_padding_mask[..., None], 0.0)
+        value = value.reshape(bs * NQ, N, H, -1)
+        offsets = self.sampling_offsets(query).view(bs, Q, H, NQ, L, P, 2)
+        attn = self.attention_weights(query).view(bs, Q, H, NQ, L * P).softmax(-1).view(bs, Q, H, NQ, L, P)
+        attn = attn.permute(0, 3, 1, 2, 4, 5).reshape(bs * NQ, Q, H, L, P).contiguous()
+        offsets = offsets.permute(0, 3, 1, 2, 4, 5, 6).reshape(bs * NQ, Q, H, L, P, 2)
+        if reference_points.shape[-1] == 2:
+            normalizer = torch.stack([spatial_shapes[..., 1], spatial_shapes[..., 0]], -1).to(offsets.dtype)
+            loc = reference_points[:, :, None, :, None, :] + offsets / normalizer[None, None, None, :, None, :]
+        elif reference_points.shape[-1] == 4:
+            loc = reference_points[:, :, None, :, None, :2] \
+                + offsets / P * reference_points[:, :, None, :, None, 2:] * 0.5
+        else:
+            raise ValueError("Last dim of reference_points must be 2 or 4, but get "
+                             f"{reference_points.shape[-1]} instead.")
+        out = MultiScaleDeformableAttnFunction_fp32.apply(value.contiguous(), spatial_shapes, level_start_index,
+                                                          loc.contiguous(), attn, self.im2col_step)
+        # mean over the previous and the current BEV (:257-262); batch element j owns rows j*NQ .. j*NQ+NQ-1
+        out = out.view(bs, NQ, Q, E).mean(1)
+        out = self.output_proj(out)
+        if not self.batch_first:
+            out = out.permute(1, 0, 2)
+        return self.dropout(out) + identity
+
+
 class SCAEncoderLayer(nn.Module):
     """cross-attention -> LayerNorm -> FFN -> LayerNorm (encoder.py:389-411 operation order without the
     temporal self-attention, which uses a different, 2-D operator)."""
@@ -264,6 +381,43 @@ class SCAEncoderLayer(nn.Module):
 
     def forward(self, query, **kw):
         query = self.norm1(self.cross_attn(query, **kw))
+        return self.norm2(query + self.ffn(query))
+
+
+class BEVFormerEncoderLayer(nn.Module):
+    """One full BEVFormer-DFA3D encoder layer: temporal self-attention -> norm -> spatial
+    cross-attention -> norm -> FFN -> norm (operation order of bevformer_base_DFA3D.py:123-124 as executed
+    by encoder.py:363-411; post-norm, so every block adds its own input as the residual)."""
+
+    def __init__(self, embed_dims=256, ffn_dims=512, num_cams=6, num_heads=8, num_levels=4, num_points=8,
+                 bev_h=200, bev_w=200, dropout=0.1):
+        super().__init__()
+        self.bev_h, self.bev_w = bev_h, bev_w
+        self.self_attn = TemporalSelfAttention(embed_dims, num_heads, num_levels=1, num_points=4,
+                                               dropout=dropout)
+        self.norm0 = nn.LayerNorm(embed_dims)
+        self.cross_attn = SpatialCrossAttention_DFA3D(
+            embed_dims, num_cams, dropout,
+            MSDeformableAttention3D_DFA3D(embed_dims, num_heads, num_levels, num_points), bev_h=bev_h,
+            bev_w=bev_w, num_head=num_heads)
+        self.norm1 = nn.LayerNorm(embed_dims)
+        self.ffn = nn.Sequential(nn.Linear(embed_dims, ffn_dims), nn.ReLU(inplace=True), nn.Dropout(dropout),
+                                 nn.Linear(ffn_dims, embed_dims), nn.Dropout(dropout))
+        self.norm2 = nn.LayerNorm(embed_dims)
+
+    def forward(self, query, prev_bev=None, bev_pos=None, ref_2d=None, **cross_kw):
+        """query (bs, bev_h*bev_w, E); prev_bev: None or (bs*2, Q, E) = [previous, current] BEV per batch
+        element (encoder.py:519-528 stacks them); ref_2d (bs*2, Q, 1, 2) (`bev_reference_points(dim="2d")`,
+        shifted for the previous BEV by the caller); cross_kw: the spatial cross-attention's inputs."""
+        dev = query.device
+        if ref_2d is None:
+            ref_2d = bev_reference_points(self.bev_h, self.bev_w, dim="2d", bs=query.shape[0] * 2, device=dev,
+                                          dtype=query.dtype)
+        shapes = torch.tensor([[self.bev_h, self.bev_w]], dtype=torch.int64, device=dev)
+        lsi = torch.zeros(1, dtype=torch.int64, device=dev)
+        query = self.norm0(self.self_attn(query, value=prev_bev, query_pos=bev_pos, reference_points=ref_2d,
+                                          spatial_shapes=shapes, level_start_index=lsi))
+        query = self.norm1(self.cross_attn(query, **cross_kw))
         return self.norm2(query + self.ffn(query))
 
 

@@ -78,8 +78,11 @@ def _gather(plan, src, width, cam_stride, batch_stride, scale):
 
 def _combine(plan, packed, width, scale):
     dst = torch.empty((plan.bs, plan.Q, width), dtype=torch.float32, device=packed.device)
+    # an empty plan has no packed rows and PyTorch gives an empty tensor no storage: hand the library some
+    # valid address instead of null (with no rows, row_of is all -1 and nothing is read through it)
+    src_ptr = packed.data_ptr() if packed.numel() else plan.inv_count.data_ptr()
     with torch.cuda.device(packed.device):
-        _lib.call_plain("dfa3d_rebatch_combine", packed.data_ptr(), plan.row_of.data_ptr(),
+        _lib.call_plain("dfa3d_rebatch_combine", src_ptr, plan.row_of.data_ptr(),
                         plan.offsets.data_ptr(), plan.cams, plan.bs, plan.Q, width,
                         None if scale is None else scale.data_ptr(), dst.data_ptr(), _stream(packed))
     return dst

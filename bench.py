@@ -236,19 +236,17 @@ class ReferenceRunner:
 
 
 # ----------------------------------------------------------------------------------------------
-def run_encoder_stack(a, rank, world, local):
-    """--workload cfg4: training step (forward, backward, gradient all-reduce, optimizer step) of the
-    6-layer spatial-cross-attention encoder stack on one frame (6 cameras) per GPU: 200x200 BEV queries,
-    each camera sees 10 000 of them, BEVFormer-base level shapes, 118 depth bins, 256-d, FFN 512.
-    Data parallel over frames with NCCL all-reduce of the projection-layer gradients (torch DDP)."""
+def measure_encoder_stack(rank, world, dev, steps, warmup):
+    """Training step (forward, backward, gradient all-reduce, optimizer step) of the 6-layer
+    spatial-cross-attention encoder stack on one frame (6 cameras) per GPU: 200x200 BEV queries, each
+    camera sees 10 000 of them, BEVFormer-base level shapes, 118 depth bins, 256-d, FFN 512.  Data
+    parallel over frames with NCCL all-reduce of the projection-layer gradients (torch DDP).  The
+    process group must exist already when world > 1.  Returns the result dict (same on every rank)."""
     from dfa3d_b200 import modules, workloads as wl
     w = wl.WORKLOADS["cfg4op"]
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist_.init_process_group("nccl", device_id=dev)
     # projection GEMMs on the TF32 tensor cores, which is what the reference's stack (PyTorch 1.9,
     # where TF32 matmuls were on by default) ran them on; the DFA3D kernels themselves stay fp32
+    tf32 = (torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32)
     torch.backends.cuda.matmul.allow_tf32 = True
     torch.backends.cudnn.allow_tf32 = True
     torch.manual_seed(0)                                   # identical initial weights on every rank
@@ -257,7 +255,7 @@ def run_encoder_stack(a, rank, world, local):
                                     num_heads=w.H, num_levels=w.L, num_points=w.P, dropout=0.1).to(dev)
     model = stack
     if world > 1:
-        model = torch.nn.parallel.DistributedDataParallel(stack, device_ids=[local],
+        model = torch.nn.parallel.DistributedDataParallel(stack, device_ids=[dev.index],
                                                           broadcast_buffers=False)
     opt = torch.optim.AdamW(stack.parameters(), lr=2e-4, weight_decay=0.01)
     g = torch.Generator().manual_seed(w.seed + 1000 * rank)
@@ -279,42 +277,55 @@ def run_encoder_stack(a, rank, world, local):
         loss = model(query, **kw).float().pow(2).mean()
         loss.backward()
         opt.step()
-        return loss
+        return loss.detach()
 
     def barrier():
         if world > 1:
             dist_.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(a.warmup):
+    for _ in range(warmup):
         step()
     barrier()
-    sampler = ClockSampler(local)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
     e0.record()
-    for _ in range(a.steps):
+    for _ in range(steps):
         loss = step()
     e1.record()
     barrier()
-    clocks = sampler.stop()
     tm = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     if world > 1:
         dist_.all_reduce(tm, op=dist_.ReduceOp.MAX)
-    ms = float(tm.item()) / a.steps
+    ms = float(tm.item()) / steps
     assert torch.isfinite(loss)
-    if rank == 0:
-        pts = w.points * layers * world
-        print(json.dumps({
-            "metric": "DFA3D fwd+bwd sampled points/s (encoder-stack training step)",
-            "value": pts / (ms * 1e-3), "unit": "sampled points/s", "n_gpus": world, "steps": a.steps,
-            "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32 (projection GEMMs tf32)", "data": "synthetic",
+    torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = tf32
+    return {"value": w.points * layers * world / (ms * 1e-3), "unit": "sampled points/s",
+            "ms_per_step": ms, "n_gpus": world, "steps": steps, "loss": float(loss),
+            "dtype": "f32 (projection GEMMs tf32)",
             "config": {"workload": "cfg4", "layers": layers, "frames_per_gpu": 1, "cameras": cams,
                        "bev_queries": bev, "queries_per_camera": w.Q, "depth_bins": w.D,
                        "embed_dims": E, "ffn_dims": 512,
                        "parallelism": f"dp{world}: NCCL all-reduce of projection gradients (DDP)"},
-            "clocks": clocks, "gpu_launches": 2 * layers * a.steps, "loss": float(loss)}), flush=True)
+            "gpu_launches": 2 * layers * steps}
+
+
+def run_encoder_stack(a, rank, world, local):
+    """--workload cfg4: the encoder-stack training step as the bench's only measurement."""
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist_.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local)
+    sampler.start()
+    r = measure_encoder_stack(rank, world, dev, a.steps, a.warmup)
+    clocks = sampler.stop()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "DFA3D fwd+bwd sampled points/s (encoder-stack training step)",
+            "value": r["value"], "unit": r["unit"], "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": r["dtype"], "data": "synthetic", "config": r["config"],
+            "clocks": clocks, "gpu_launches": r["gpu_launches"], "loss": r["loss"]}), flush=True)
     if world > 1:
         dist_.destroy_process_group()
 
@@ -536,6 +547,7 @@ def main():
     d = wl.make_inputs(w, seed=w.seed + 1000 * rank)
     t = {k: v.to(dev) for k, v in d.items()}
     runner = OursRunner(w, t) if a.impl == "ours" else ReferenceRunner(w, t, ref)
+    launches_per_step = runner.launches_per_step
 
     def step(events=None):
         if events is not None:
@@ -604,9 +616,12 @@ def main():
                 extra["query_blocks"] = {"error": f"adjoint identity violated: {e}"}
         if rank == 0 and w.L * w.P == 32 and w.H == 8 and w.C == 32 and w.value_dtype == "fp32":
             extra["memory_stream_floor"] = memory_stream_floor(w)
+        if w.name == "cfg2":
+            # the training configuration: 6-layer spatial-cross-attention encoder stack, one frame per GPU
+            extra["encoder_stack"] = measure_encoder_stack(rank, world, dev, 5, 2)
 
     if rank == 0:
-        report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e, extra)
+        report(a, w, world, launches_per_step, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e, extra)
     if world > 1:
         dist_.destroy_process_group()
 
@@ -683,6 +698,8 @@ def measure_extras(a, w, dev, world, rank, barrier):
                          "fwd_bwd_ms": s_ms, "fwd_bwd_points_per_s": w3.points * world / (s_ms * 1e-3)}
         del r3
     return extra
+
+
 def memory_stream_floor(w):
     """Lower bounds of the two kernels from the measured rates of the memory primitives they are made
     of (dfa3d_b200.rates replays a launch's address stream without the arithmetic)."""
@@ -697,7 +714,7 @@ def memory_stream_floor(w):
         return {"unavailable": str(e)}
 
 
-def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e, extra=None):
+def report(a, w, world, launches_per_step, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e, extra=None):
     peak, peak_src = measured_peak_gbs()
     fwd_b, bwd_b = w.algorithmic_bytes()
     traffic = NCU_DRAM_TRAFFIC.get(w.name, {})
@@ -716,7 +733,7 @@ def report(a, w, world, runner, value, ms_per_step, fwd_ms, bwd_ms, clocks, e2e,
                           "parity-sized workload, not a bandwidth measurement" % (fwd_b / 1e6))},
         "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
         "clocks": clocks,
-        "gpu_launches": runner.launches_per_step * a.steps,
+        "gpu_launches": launches_per_step * a.steps,
         "e2e": e2e,
     }
     if a.impl == "ours":

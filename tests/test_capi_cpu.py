@@ -93,6 +93,19 @@ def test_validation_returns_codes_not_crashes(lib_built):
     assert lib.dfa3d_rebatch_gather(None, None, None, None, 2, 1, 4, 0, 0, 4, None, None, 8, None) == -1
     assert lib.dfa3d_rebatch_combine(None, None, None, 2, 1, 0, 8, None, None, None) == 0
     assert lib.dfa3d_rebatch_combine(None, None, None, 2, 1, 4, 8, None, None, None) == -1
+    # depth-distribution producer: logits, B, D, map_h, map_w, shapes, shape_stride, level_start, L, N,
+    # activation, dist_dtype, dist, stream
+    prod = lib.dfa3d_dist_from_logits
+    assert prod(None, 0, 64, 4, 4, None, 2, None, 1, 16, 0, 0, None, None) == 0          # B = 0: nothing to do
+    assert prod(None, 1, 64, 4, 4, None, 2, None, 1, 16, 0, 0, None, None) == -1 and b"logits" in lib.dfa3d_last_error()
+    assert prod(None, 1, 257, 4, 4, None, 2, None, 1, 16, 0, 0, None, None) == -2 and b"256" in lib.dfa3d_last_error()
+    assert prod(None, 1, 64, 4, 4, None, 2, None, 1, 16, 5, 0, None, None) == -1 and b"activation" in lib.dfa3d_last_error()
+    assert prod(None, 1, 64, 4, 4, None, 4, None, 1, 16, 0, 0, None, None) == -1 and b"shape_stride" in lib.dfa3d_last_error()
+    assert prod(None, 1, 64, 4, 4, None, 2, None, 1, 16, 0, 3, None, None) == -1 and b"dist_dtype" in lib.dfa3d_last_error()
+    assert lib.dfa3d_dist_from_logits_backward(None, 1, 64, 0, 4, None, 2, None, 1, 16, 0, None, None, None) == -1
+    # a dist map needs both of its sizes
+    bad = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, 0, 0, 2, 3, 0)
+    assert lib.dfa3d_fused_forward(ctypes.byref(bad), *([None] * 9)) == -1 and b"dist_map" in lib.dfa3d_last_error()
     # the anchors must divide the points per level
     assert lib.dfa3d_attn3d_forward(ctypes.byref(ok), 3, *([None] * 10)) == -1
     assert b"num_anchors" in lib.dfa3d_last_error()
@@ -130,3 +143,37 @@ def test_missing_library_fails_loudly(tmp_path):
     env = dict(os.environ, DFA3D_B200_LIB=str(tmp_path / "absent.so"))
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env)
     assert r.returncode == 0 and "raised" in r.stdout, r.stderr
+
+
+def test_header_is_plain_c_and_the_library_links_from_c(lib_built, tmp_path):
+    """include/dfa3d_b200.h compiles as C99 with warnings as errors, and a C program linked against
+    the shared library can call it (version query and an argument check; no GPU needed)."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    src = tmp_path / "use_abi.c"
+    src.write_text(r"""
+#include <stdio.h>
+#include <string.h>
+#include "dfa3d_b200.h"
+int main(void) {
+  dfa3d_problem p;
+  memset(&p, 0, sizeof p);
+  p.B = 1; p.N = 4; p.H = 1; p.C = 4; p.D = 2; p.L = 1; p.Q = 1; p.P = 1; p.dist_head_stride = 2;
+  if (dfa3d_abi_version() != DFA3D_ABI_VERSION) return 1;
+  if (dfa3d_fused_forward(&p, 0, 0, 0, 0, 0, 0, 0, 0, 0) != DFA3D_ERR_INVALID_ARGUMENT) return 2;
+  if (!strstr(dfa3d_last_error(), "value")) return 3;
+  if (sizeof(dfa3d_problem) != 56) return 4;
+  printf("abi %d ok\n", dfa3d_abi_version());
+  return 0;
+}
+""")
+    exe = tmp_path / "use_abi"
+    libdir = os.path.dirname(lib_built)
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+                        str(src), "-o", str(exe), "-L", libdir, "-ldfa3d_b200", f"-Wl,-rpath,{libdir}"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and "ok" in r.stdout, (r.returncode, r.stdout, r.stderr)

@@ -315,3 +315,103 @@ def test_encoder_stack_training_step_matches_grid_sample_form(lib_built, monkeyp
         assert torch.isfinite(got[2][n]).all()
         torch.testing.assert_close(got[2][n], want[2][n], rtol=2e-3, atol=1e-4, msg=lambda m, n=n: f"{n}: {m}")
         torch.testing.assert_close(got[3][n], want[3][n], rtol=1e-4, atol=1e-5, msg=lambda m, n=n: f"{n}: {m}")
+
+
+def test_spatial_cross_attention_when_no_camera_sees_anything(lib_built):
+    """Empty plan (zero packed rows): the layer reduces to output_proj(0) + residual, gradients flow to
+    the residual path only, and nothing is launched with an empty grid."""
+    torch.manual_seed(3)
+    sca = modules.SpatialCrossAttention_DFA3D(embed_dims=32, num_cams=3, dropout=0.0,
+                                              deformable_attention=modules.MSDeformableAttention3D_DFA3D(
+                                                  embed_dims=32, num_heads=2, num_levels=2, num_points=8)).to(DEV)
+    d = _inputs(9, bs=2)
+    d["bev_mask"][:] = False
+    q = d["query"].clone().requires_grad_(True)
+    out = sca(q, None, d["value"], d["value_dpt_dist"], d["reference_points_cam"], d["bev_mask"],
+              d["spatial_shapes"], d["level_start_index"])
+    torch.testing.assert_close(out, q.detach() + sca.output_proj.bias.detach().expand_as(q))
+    out.sum().backward()
+    torch.testing.assert_close(q.grad, torch.ones_like(q))
+
+
+class _MsdaGridSampleOp:
+    """Stand-in with the 2-D Function's call signature: per-level 4-D grid_sample."""
+
+    @staticmethod
+    def apply(value, shapes2, lsi, loc, attn, im2col_step):
+        return G.msda_grid_sample(value.double(), shapes2.tolist(), lsi.tolist(), loc.double(),
+                                  attn.double()).to(value.dtype)
+
+
+@pytest.mark.parametrize("with_prev,batch_first", [(True, True), (False, True), (True, False)])
+def test_temporal_self_attention_matches_grid_sample_form(lib_built, monkeypatch, with_prev, batch_first):
+    """TemporalSelfAttention (previous + current BEV, plain 2-D deformable attention on the depth-weighted
+    kernels) against the same module with the 4-D grid_sample operator: output, query gradient, every
+    parameter gradient (temporal_self_attention.py:130-272)."""
+    bev_h, bev_w, E, H, P, bs = 8, 10, 32, 4, 4, 2
+    Q = bev_h * bev_w
+    g = torch.Generator().manual_seed(21)
+    query = torch.randn(bs, Q, E, generator=g).to(DEV)
+    prev = torch.randn(bs, Q, E, generator=g).to(DEV)
+    pos = torch.randn(bs, Q, E, generator=g).to(DEV)
+    refp = torch.rand(bs * 2, Q, 1, 2, generator=g).to(DEV) * 1.1 - 0.05
+    shapes = torch.tensor([[bev_h, bev_w]], dtype=torch.int64, device=DEV)
+    lsi = torch.zeros(1, dtype=torch.int64, device=DEV)
+
+    def run():
+        torch.manual_seed(5)
+        tsa = modules.TemporalSelfAttention(embed_dims=E, num_heads=H, num_levels=1, num_points=P, dropout=0.0,
+                                            batch_first=batch_first).to(DEV)
+        with torch.no_grad():
+            tsa.sampling_offsets.weight.normal_(0, 0.05)
+            tsa.attention_weights.weight.normal_(0, 0.05)
+        q = query.clone().requires_grad_(True)
+        value = torch.stack([prev, q], 1).reshape(bs * 2, Q, E) if with_prev else None
+        qq, pp = (q, pos) if batch_first else (q.permute(1, 0, 2), pos.permute(1, 0, 2))
+        vv = value if (value is None or batch_first) else value.permute(1, 0, 2)
+        out = tsa(qq, value=vv, query_pos=pp, reference_points=refp, spatial_shapes=shapes, level_start_index=lsi)
+        assert out.shape == qq.shape
+        out.pow(2).sum().backward()
+        out = out if batch_first else out.permute(1, 0, 2)
+        return out.detach(), q.grad.clone(), {n: p.grad.clone() for n, p in tsa.named_parameters()}
+
+    got = run()
+    monkeypatch.setattr(modules, "MultiScaleDeformableAttnFunction_fp32", _MsdaGridSampleOp)
+    want = run()
+    torch.testing.assert_close(got[0], want[0], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(got[1], want[1], rtol=1e-3, atol=1e-4)
+    for n in want[2]:
+        torch.testing.assert_close(got[2][n], want[2][n], rtol=1e-3, atol=1e-4, msg=lambda m, n=n: f"{n}: {m}")
+
+
+def test_full_encoder_layer_is_the_composition_of_its_blocks(lib_built):
+    """BEVFormerEncoderLayer = temporal self-attention -> norm -> spatial cross-attention -> norm -> FFN ->
+    norm (encoder.py:363-411): its output equals the blocks applied by hand, and every parameter gets a
+    finite gradient."""
+    torch.manual_seed(7)
+    bev_h, bev_w, E = 5, 10, 32
+    layer = modules.BEVFormerEncoderLayer(embed_dims=E, ffn_dims=64, num_cams=3, num_heads=2, num_levels=2,
+                                          num_points=8, bev_h=bev_h, bev_w=bev_w, dropout=0.0).to(DEV)
+    _randomise(layer.cross_attn.deformable_attention)
+    d = _inputs(17, bs=1, Q=bev_h * bev_w)
+    kw = dict(key=None, value=d["value"], value_dpt_dist=d["value_dpt_dist"],
+              reference_points_cam=d["reference_points_cam"], bev_mask=d["bev_mask"],
+              spatial_shapes=d["spatial_shapes"], level_start_index=d["level_start_index"])
+    g = torch.Generator().manual_seed(2)
+    prev = torch.randn(2, bev_h * bev_w, E, generator=g).to(DEV)
+    pos = torch.randn(1, bev_h * bev_w, E, generator=g).to(DEV)
+    q = d["query"].clone().requires_grad_(True)
+    out = layer(q, prev_bev=prev, bev_pos=pos, **kw)
+    with torch.no_grad():
+        ref2d = modules.bev_reference_points(bev_h, bev_w, dim="2d", bs=2, device=DEV)
+        shapes = torch.tensor([[bev_h, bev_w]], dtype=torch.int64, device=DEV)
+        x = layer.norm0(layer.self_attn(d["query"], value=prev, query_pos=pos, reference_points=ref2d,
+                                        spatial_shapes=shapes, level_start_index=torch.zeros(1, dtype=torch.int64,
+                                                                                             device=DEV)))
+        x = layer.norm1(layer.cross_attn(x, **kw))
+        want = layer.norm2(x + layer.ffn(x))
+    torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-6)
+    out.pow(2).mean().backward()
+    assert torch.isfinite(q.grad).all() and q.grad.abs().sum() > 0
+    for n, p in layer.named_parameters():
+        assert p.grad is not None and torch.isfinite(p.grad).all(), n

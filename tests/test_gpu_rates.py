@@ -1,5 +1,5 @@
 """The memory-primitive rate probes run and report plausible figures (they are what the kernels' lower
-bounds in the bench line and in profiles/ are derived from)."""
+bounds in the bench line are derived from)."""
 import pytest
 import torch
 

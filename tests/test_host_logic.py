@@ -205,3 +205,18 @@ def test_camera_query_grid_covers_every_camera_query_pair_once():
     assert sharding.camera_query_grid(6, 2, 1)[3:] == (0, 1)
     with pytest.raises(ValueError):
         sharding.camera_query_grid(6, 8, 0, camera_groups=3)
+
+
+def test_bev_reference_points_are_cell_and_pillar_centres():
+    """modules.bev_reference_points against the closed forms of encoder.py:61-99."""
+    H, W, Z, n, bs = 3, 5, 8, 4, 2
+    r3 = modules.bev_reference_points(H, W, Z, n, "3d", bs, "cpu")
+    r2 = modules.bev_reference_points(H, W, dim="2d", bs=bs, device="cpu")
+    assert r3.shape == (bs, n, H * W, 3) and r2.shape == (bs, H * W, 1, 2)
+    for y in range(H):
+        for x in range(W):
+            q = y * W + x
+            assert torch.allclose(r2[1, q, 0], torch.tensor([(x + 0.5) / W, (y + 0.5) / H]))
+            for k in range(n):
+                z = (0.5 + k * (Z - 1.0) / (n - 1)) / Z
+                assert torch.allclose(r3[0, k, q], torch.tensor([(x + 0.5) / W, (y + 0.5) / H, z]))
