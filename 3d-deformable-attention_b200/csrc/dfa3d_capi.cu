@@ -380,9 +380,11 @@ int dfa3d_rebatch_plan(const uint8_t *bev_mask, int32_t cams, int32_t bs, int32_
                 cams, bs, Z, Q);
   if ((long long)cams * Q >= (1LL << 31) || (long long)bs * cams * Q >= (1LL << 31))
     return fail(DFA3D_ERR_UNSUPPORTED, "bs * cams * Q must stay below 2^31");
-  REQUIRE_PTR(counts); REQUIRE_PTR(offsets); REQUIRE_PTR(op_offsets); REQUIRE_PTR(packed_query);
-  REQUIRE_PTR(packed_camera); REQUIRE_PTR(row_of); REQUIRE_PTR(inv_count);
-  if (Q > 0) REQUIRE_PTR(bev_mask);
+  REQUIRE_PTR(counts); REQUIRE_PTR(offsets); REQUIRE_PTR(op_offsets);
+  if (Q > 0) {      // with no queries the per-query tables are empty and may have no storage
+    REQUIRE_PTR(bev_mask); REQUIRE_PTR(packed_query); REQUIRE_PTR(packed_camera); REQUIRE_PTR(row_of);
+    REQUIRE_PTR(inv_count);
+  }
   return finish(dfa3d::launch_rebatch_plan(bev_mask, cams, bs, Q, Z, counts, offsets, op_offsets,
                                            packed_query, packed_camera, row_of, inv_count,
                                            (cudaStream_t)stream),
