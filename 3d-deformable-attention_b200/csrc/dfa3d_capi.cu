@@ -470,4 +470,98 @@ int dfa3d_dist_from_logits_backward(const float *logits, int32_t B, int32_t D, i
                 "dfa3d_dist_from_logits_backward launch");
 }
 
+// ---- double precision -------------------------------------------------------------------------
+// Same checks as check_problem(); both dtype fields must say DFA3D_DTYPE_F64 and dist must be laid out
+// like value (no single-map option in double).
+static int check_problem64(const dfa3d_problem *p, bool need_value, bool need_dist) {
+  if (!p) return fail(DFA3D_ERR_INVALID_ARGUMENT, "problem descriptor is null");
+  if ((need_value && p->value_dtype != DFA3D_DTYPE_F64) || (need_dist && p->dist_dtype != DFA3D_DTYPE_F64))
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "the *_f64 entry points take DFA3D_DTYPE_F64 tensors only");
+  if (p->dist_map_h != 0 || p->dist_map_w != 0)
+    return fail(DFA3D_ERR_UNSUPPORTED, "the single-map dist option is not available in double precision");
+  dfa3d_problem q = *p;
+  q.value_dtype = DFA3D_DTYPE_F32; q.dist_dtype = DFA3D_DTYPE_F32;   // the size checks are type-independent
+  return check_problem(&q, need_value, need_dist);
+}
+
+int dfa3d_depth_score_forward_f64(const dfa3d_problem *p, const double *dist, const int64_t *shapes3,
+                                  const int64_t *level_start, const double *loc3, double *depth_score,
+                                  void *stream) {
+  if (int rc = check_problem64(p, false, true)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start); REQUIRE_PTR(loc3);
+  REQUIRE_PTR(depth_score);
+  return finish(dfa3d::launch_depth_forward64(p, dist, shapes3, level_start, loc3, depth_score,
+                                              (cudaStream_t)stream),
+                "dfa3d_depth_score_forward_f64 launch");
+}
+
+int dfa3d_depth_score_backward_f64(const dfa3d_problem *p, const double *dist, const int64_t *shapes3,
+                                   const int64_t *level_start, const double *loc3,
+                                   const double *grad_depth_score, double *grad_dist, double *grad_loc3,
+                                   void *stream) {
+  if (int rc = check_problem64(p, false, true)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start); REQUIRE_PTR(loc3);
+  REQUIRE_PTR(grad_depth_score); REQUIRE_PTR(grad_dist); REQUIRE_PTR(grad_loc3);
+  return finish(dfa3d::launch_depth_backward64(p, dist, shapes3, level_start, loc3, grad_depth_score,
+                                               grad_dist, grad_loc3, (cudaStream_t)stream),
+                "dfa3d_depth_score_backward_f64 launch");
+}
+
+int dfa3d_wms_attn_forward_f64(const dfa3d_problem *p, const double *value, const int64_t *shapes2,
+                               const int64_t *level_start, const double *loc2, const double *attn,
+                               const double *depth_score, double *out, void *stream) {
+  if (int rc = check_problem64(p, true, false)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(shapes2); REQUIRE_PTR(level_start); REQUIRE_PTR(loc2);
+  REQUIRE_PTR(attn); REQUIRE_PTR(depth_score); REQUIRE_PTR(out);
+  return finish(dfa3d::launch_forward64(p, value, nullptr, shapes2, 2, level_start, loc2, 2, attn,
+                                        depth_score, false, out, nullptr, (cudaStream_t)stream),
+                "dfa3d_wms_attn_forward_f64 launch");
+}
+
+int dfa3d_wms_attn_backward_f64(const dfa3d_problem *p, const double *value, const int64_t *shapes2,
+                                const int64_t *level_start, const double *loc2, const double *attn,
+                                const double *depth_score, const double *grad_out, double *grad_value,
+                                double *grad_loc2, double *grad_attn, double *grad_depth_score,
+                                void *stream) {
+  if (int rc = check_problem64(p, true, false)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(shapes2); REQUIRE_PTR(level_start); REQUIRE_PTR(loc2);
+  REQUIRE_PTR(attn); REQUIRE_PTR(depth_score); REQUIRE_PTR(grad_out); REQUIRE_PTR(grad_value);
+  REQUIRE_PTR(grad_loc2); REQUIRE_PTR(grad_attn); REQUIRE_PTR(grad_depth_score);
+  return finish(dfa3d::launch_backward64(p, value, nullptr, shapes2, 2, level_start, loc2, 2, attn,
+                                         depth_score, false, grad_out, grad_value, nullptr, grad_loc2,
+                                         grad_attn, grad_depth_score, (cudaStream_t)stream),
+                "dfa3d_wms_attn_backward_f64 launch");
+}
+
+int dfa3d_fused_forward_f64(const dfa3d_problem *p, const double *value, const double *dist,
+                            const int64_t *shapes3, const int64_t *level_start, const double *loc3,
+                            const double *attn, double *out, double *depth_score_out, void *stream) {
+  if (int rc = check_problem64(p, true, true)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start);
+  REQUIRE_PTR(loc3); REQUIRE_PTR(attn); REQUIRE_PTR(out);
+  return finish(dfa3d::launch_forward64(p, value, dist, shapes3, 3, level_start, loc3, 3, attn, nullptr,
+                                        true, out, depth_score_out, (cudaStream_t)stream),
+                "dfa3d_fused_forward_f64 launch");
+}
+
+int dfa3d_fused_backward_f64(const dfa3d_problem *p, const double *value, const double *dist,
+                             const int64_t *shapes3, const int64_t *level_start, const double *loc3,
+                             const double *attn, const double *grad_out, double *grad_value,
+                             double *grad_dist, double *grad_loc3, double *grad_attn, void *stream) {
+  if (int rc = check_problem64(p, true, true)) return rc;
+  if (p->B == 0 || p->Q == 0) return DFA3D_OK;
+  REQUIRE_PTR(value); REQUIRE_PTR(dist); REQUIRE_PTR(shapes3); REQUIRE_PTR(level_start);
+  REQUIRE_PTR(loc3); REQUIRE_PTR(attn); REQUIRE_PTR(grad_out); REQUIRE_PTR(grad_value);
+  REQUIRE_PTR(grad_dist); REQUIRE_PTR(grad_loc3); REQUIRE_PTR(grad_attn);
+  return finish(dfa3d::launch_backward64(p, value, dist, shapes3, 3, level_start, loc3, 3, attn, nullptr,
+                                         true, grad_out, grad_value, grad_dist, grad_loc3, grad_attn,
+                                         nullptr, (cudaStream_t)stream),
+                "dfa3d_fused_backward_f64 launch");
+}
+
 }  // extern "C"

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+struct dfa3d_problem;
 namespace dfa3d {
 struct KArgs;
 // mode: dfa3d::Mode
@@ -22,6 +23,24 @@ cudaError_t launch_rebatch_gather(const float *src, const int32_t *packed_query,
 cudaError_t launch_rebatch_combine(const float *src, const int32_t *row_of, const int32_t *offsets,
                                    int cams, int bs, int Q, int W, const float *scale, float *dst,
                                    cudaStream_t s);
+// double-precision kernels (dfa3d_fp64.cu); `from_dist`: depth scores are sampled from dist (one-stage)
+// instead of being given (two-stage attention; a null ds_in then means all ones)
+cudaError_t launch_forward64(const dfa3d_problem *p, const double *value, const double *dist,
+                             const int64_t *shapes, int shape_stride, const int64_t *lsi,
+                             const double *loc, int loc_stride, const double *attn, const double *ds_in,
+                             bool from_dist, double *out, double *ds_out, cudaStream_t s);
+cudaError_t launch_backward64(const dfa3d_problem *p, const double *value, const double *dist,
+                              const int64_t *shapes, int shape_stride, const int64_t *lsi,
+                              const double *loc, int loc_stride, const double *attn, const double *ds_in,
+                              bool from_dist, const double *grad_out, double *grad_value,
+                              double *grad_dist, double *grad_loc, double *grad_attn, double *grad_ds_out,
+                              cudaStream_t s);
+cudaError_t launch_depth_forward64(const dfa3d_problem *p, const double *dist, const int64_t *shapes3,
+                                   const int64_t *lsi, const double *loc3, double *ds_out,
+                                   cudaStream_t s);
+cudaError_t launch_depth_backward64(const dfa3d_problem *p, const double *dist, const int64_t *shapes3,
+                                    const int64_t *lsi, const double *loc3, const double *grad_ds,
+                                    double *grad_dist, double *grad_loc3, cudaStream_t s);
 // depth-distribution producer (dfa3d_dist_producer.cu)
 int dist_producer_max_bins();
 cudaError_t launch_dist_from_logits(const float *logits, const int64_t *shapes, int shape_stride,

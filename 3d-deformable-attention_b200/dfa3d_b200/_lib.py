@@ -12,6 +12,7 @@ LIB_PATH = os.environ.get("DFA3D_B200_LIB") or os.path.join(_HERE, "libdfa3d_b20
 ABI_VERSION = 2
 DTYPE_F32 = 0
 DTYPE_BF16 = 1
+DTYPE_F64 = 2
 MAX_LEVELS = 32
 MAX_CHANNELS = 1024
 
@@ -43,6 +44,13 @@ ENTRY_POINTS = {
     "dfa3d_fused_backward": 12,
     "dfa3d_msda_forward": 7,
     "dfa3d_msda_backward": 10,
+    # double-precision instantiations (same argument lists)
+    "dfa3d_depth_score_forward_f64": 6,
+    "dfa3d_depth_score_backward_f64": 8,
+    "dfa3d_wms_attn_forward_f64": 8,
+    "dfa3d_wms_attn_backward_f64": 12,
+    "dfa3d_fused_forward_f64": 9,
+    "dfa3d_fused_backward_f64": 12,
     # ragged variants: the query-offset table is one more pointer, right after the descriptor
     "dfa3d_fused_forward_ragged": 10,
     "dfa3d_fused_backward_ragged": 13,

@@ -41,12 +41,25 @@ def _step_check(batch, im2col_step):
 
 
 _F32 = (torch.float32,)
+_F64 = (torch.float64,)
 _VAL = (torch.float32, torch.bfloat16)
 _I64 = (torch.int64,)
 
 
 def _dt(t):
+    if t.dtype == torch.float64:
+        return _lib.DTYPE_F64
     return _lib.DTYPE_BF16 if t.dtype == torch.bfloat16 else _lib.DTYPE_F32
+
+
+def _types(t, dist_map=None):
+    """(dtypes allowed for value/dist, dtypes allowed for everything else, output dtype, entry-point
+    suffix) chosen by the scalar type of the call's main tensor."""
+    if t.dtype == torch.float64:
+        if dist_map is not None:
+            raise RuntimeError("dist_map is not available in double precision")
+        return _F64, _F64, torch.float64, "_f64"
+    return _VAL, _F32, torch.float32, ""
 
 
 def _ptr(t):
@@ -117,9 +130,10 @@ def ms_depth_score_sample_forward(value, value_spatial_shapes, value_level_start
     """`value` is the depth distribution (B,N,H,D) [or (B,N,D)]; returns depth_score (B,Q,H,L,P,4).
     dist_map=(h, w): `value` is one h x w map per camera that every level reads with nearest indexing."""
     dist = value
-    _chk(dist, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    VAL, F, odt, sfx = _types(dist, dist_map)
+    _chk(dist, "value", VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
     _chk(value_level_start_index, "level_start_index", _I64)
-    _chk(sampling_locations, "sampling_loc", _F32)
+    _chk(sampling_locations, "sampling_loc", F)
     _same_device(dist, value_spatial_shapes, value_level_start_index, sampling_locations)
     B, Q, H, L, P = _loc_dims(sampling_locations, 3)
     Bd, N, D, hs = _dist_problem(dist, H)
@@ -127,11 +141,11 @@ def ms_depth_score_sample_forward(value, value_spatial_shapes, value_level_start
         raise RuntimeError("inconsistent shapes between value, spatial_shapes (L,3) and sampling_loc")
     _level_table(value_spatial_shapes, value_level_start_index, L, 3)
     _step_check(B, im2col_step)
-    out = torch.empty((B, Q, H, L, P, 4), dtype=torch.float32, device=dist.device)
+    out = torch.empty((B, Q, H, L, P, 4), dtype=odt, device=dist.device)
     N = _level_pixels(N, dist_map, value_spatial_shapes)
     pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs, *_map(dist_map))
     with torch.cuda.device(dist.device):
-        _lib.call("dfa3d_depth_score_forward", pr, _ptr(dist), _ptr(value_spatial_shapes),
+        _lib.call("dfa3d_depth_score_forward" + sfx, pr, _ptr(dist), _ptr(value_spatial_shapes),
                   _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(out), _stream(dist))
     return out
 
@@ -142,10 +156,11 @@ def ms_depth_score_sample_backward(value, value_spatial_shapes, value_level_star
     """Accumulates into grad_value (layout of `value`, float32, caller-zeroed) and overwrites
     grad_sampling_loc (B,Q,H,L,P,3) with (0, 0, dL/dz)."""
     dist = value
-    _chk(dist, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    VAL, F, odt, sfx = _types(dist, dist_map)
+    _chk(dist, "value", VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
     _chk(value_level_start_index, "level_start_index", _I64)
-    _chk(sampling_locations, "sampling_loc", _F32); _chk(grad_output, "grad_output", _F32)
-    _chk(grad_value, "grad_value", _F32); _chk(grad_sampling_loc, "grad_sampling_loc", _F32)
+    _chk(sampling_locations, "sampling_loc", F); _chk(grad_output, "grad_output", F)
+    _chk(grad_value, "grad_value", F); _chk(grad_sampling_loc, "grad_sampling_loc", F)
     _same_device(dist, value_spatial_shapes, value_level_start_index, sampling_locations, grad_output,
                  grad_value, grad_sampling_loc)
     B, Q, H, L, P = _loc_dims(sampling_locations, 3)
@@ -160,18 +175,19 @@ def ms_depth_score_sample_backward(value, value_spatial_shapes, value_level_star
     N = _level_pixels(N, dist_map, value_spatial_shapes)
     pr = _lib.Problem(B, N, H, 0, D, L, Q, P, _lib.DTYPE_F32, _dt(dist), hs, *_map(dist_map))
     with torch.cuda.device(dist.device):
-        _lib.call("dfa3d_depth_score_backward", pr, _ptr(dist), _ptr(value_spatial_shapes),
+        _lib.call("dfa3d_depth_score_backward" + sfx, pr, _ptr(dist), _ptr(value_spatial_shapes),
                   _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(grad_output),
                   _ptr(grad_value), _ptr(grad_sampling_loc), _stream(dist))
 
 
 def wms_deform_attn_forward(value, value_spatial_shapes, value_level_start_index, sampling_locations,
                             attention_weights, depth_scores, im2col_step):
-    """Returns output (B,Q,H*C) float32."""
-    _chk(value, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    """Returns output (B,Q,H*C), float32 (float64 for float64 inputs)."""
+    VAL, F, odt, sfx = _types(value)
+    _chk(value, "value", VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
     _chk(value_level_start_index, "level_start_index", _I64)
-    _chk(sampling_locations, "sampling_loc", _F32); _chk(attention_weights, "attn_weight", _F32)
-    _chk(depth_scores, "depth_score", _F32)
+    _chk(sampling_locations, "sampling_loc", F); _chk(attention_weights, "attn_weight", F)
+    _chk(depth_scores, "depth_score", F)
     _same_device(value, value_spatial_shapes, value_level_start_index, sampling_locations,
                  attention_weights, depth_scores)
     B, N, H, C = value.shape
@@ -183,10 +199,10 @@ def wms_deform_attn_forward(value, value_spatial_shapes, value_level_start_index
                            "attn_weight and depth_score")
     _level_table(value_spatial_shapes, value_level_start_index, L, 2)
     _step_check(B, im2col_step)
-    out = torch.empty((B, Q, H * C), dtype=torch.float32, device=value.device)
+    out = torch.empty((B, Q, H * C), dtype=odt, device=value.device)
     pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
     with torch.cuda.device(value.device):
-        _lib.call("dfa3d_wms_attn_forward", pr, _ptr(value), _ptr(value_spatial_shapes),
+        _lib.call("dfa3d_wms_attn_forward" + sfx, pr, _ptr(value), _ptr(value_spatial_shapes),
                   _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(attention_weights),
                   _ptr(depth_scores), _ptr(out), _stream(value))
     return out
@@ -196,12 +212,13 @@ def wms_deform_attn_backward(value, value_spatial_shapes, value_level_start_inde
                              attention_weights, depth_scores, grad_output, grad_value,
                              grad_sampling_loc, grad_attn_weight, grad_depth_score, im2col_step):
     """Accumulates into grad_value (float32, caller-zeroed); overwrites the other three."""
-    _chk(value, "value", _VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
+    VAL, F, odt, sfx = _types(value)
+    _chk(value, "value", VAL); _chk(value_spatial_shapes, "spatial_shapes", _I64)
     _chk(value_level_start_index, "level_start_index", _I64)
-    _chk(sampling_locations, "sampling_loc", _F32); _chk(attention_weights, "attn_weight", _F32)
-    _chk(depth_scores, "depth_score", _F32); _chk(grad_output, "grad_output", _F32)
-    _chk(grad_value, "grad_value", _F32); _chk(grad_sampling_loc, "grad_sampling_loc", _F32)
-    _chk(grad_attn_weight, "grad_attn_weight", _F32); _chk(grad_depth_score, "grad_depth_score", _F32)
+    _chk(sampling_locations, "sampling_loc", F); _chk(attention_weights, "attn_weight", F)
+    _chk(depth_scores, "depth_score", F); _chk(grad_output, "grad_output", F)
+    _chk(grad_value, "grad_value", F); _chk(grad_sampling_loc, "grad_sampling_loc", F)
+    _chk(grad_attn_weight, "grad_attn_weight", F); _chk(grad_depth_score, "grad_depth_score", F)
     _same_device(value, value_spatial_shapes, value_level_start_index, sampling_locations,
                  attention_weights, depth_scores, grad_output, grad_value, grad_sampling_loc,
                  grad_attn_weight, grad_depth_score)
@@ -217,7 +234,7 @@ def wms_deform_attn_backward(value, value_spatial_shapes, value_level_start_inde
     _step_check(B, im2col_step)
     pr = _lib.Problem(B, N, H, C, 1, L, Q, P, _dt(value), _lib.DTYPE_F32, 0)
     with torch.cuda.device(value.device):
-        _lib.call("dfa3d_wms_attn_backward", pr, _ptr(value), _ptr(value_spatial_shapes),
+        _lib.call("dfa3d_wms_attn_backward" + sfx, pr, _ptr(value), _ptr(value_spatial_shapes),
                   _ptr(value_level_start_index), _ptr(sampling_locations), _ptr(attention_weights),
                   _ptr(depth_scores), _ptr(grad_output), _ptr(grad_value), _ptr(grad_sampling_loc),
                   _ptr(grad_attn_weight), _ptr(grad_depth_score), _stream(value))
@@ -286,9 +303,10 @@ def ms_deform_attn_backward(value, value_spatial_shapes, value_level_start_index
 # one-stage autograd Function)
 # ------------------------------------------------------------------------------------------------
 def _fused_problem(value, dist, shapes3, lsi, loc3, attn, dist_map=None):
-    _chk(value, "value", _VAL); _chk(dist, "value_dpt_dist", _VAL)
+    VAL, F, _, _ = _types(value, dist_map)
+    _chk(value, "value", VAL); _chk(dist, "value_dpt_dist", VAL)
     _chk(shapes3, "spatial_shapes", _I64); _chk(lsi, "level_start_index", _I64)
-    _chk(loc3, "sampling_loc", _F32); _chk(attn, "attn_weight", _F32)
+    _chk(loc3, "sampling_loc", F); _chk(attn, "attn_weight", F)
     _same_device(value, dist, shapes3, lsi, loc3, attn)
     B, N, H, C = value.shape
     Bq, Q, Hq, L, P = _loc_dims(loc3, 3)
@@ -314,16 +332,17 @@ def dfa3d_fused_forward(value, value_dpt_dist, value_spatial_shapes, value_level
                                             attention_weights, dist_map)
     _step_check(B, im2col_step)
     dev = value.device
+    _, F, odt, sfx = _types(value, dist_map)
     if out is None:
-        out = torch.empty((B, Q, H * C), dtype=torch.float32, device=dev)
+        out = torch.empty((B, Q, H * C), dtype=odt, device=dev)
     else:
-        _chk(out, "out", _F32)
+        _chk(out, "out", F)
         _same_device(value, out)
         if out.numel() != B * Q * H * C:
             raise RuntimeError("out has the wrong number of elements")
-    ds = torch.empty((B, Q, H, L, P, 4), dtype=torch.float32, device=dev) if need_depth_score else None
+    ds = torch.empty((B, Q, H, L, P, 4), dtype=odt, device=dev) if need_depth_score else None
     with torch.cuda.device(dev):
-        _lib.call("dfa3d_fused_forward", pr, _ptr(value), _ptr(value_dpt_dist),
+        _lib.call("dfa3d_fused_forward" + sfx, pr, _ptr(value), _ptr(value_dpt_dist),
                   _ptr(value_spatial_shapes), _ptr(value_level_start_index),
                   _ptr(sampling_locations), _ptr(attention_weights), _ptr(out), _ptr(ds),
                   _stream(value))
@@ -339,10 +358,11 @@ def dfa3d_fused_backward(value, value_dpt_dist, value_spatial_shapes, value_leve
     pr, (B, Q, H, L, P, C) = _fused_problem(value, value_dpt_dist, value_spatial_shapes,
                                             value_level_start_index, sampling_locations,
                                             attention_weights, dist_map)
+    _, F, _, sfx = _types(value, dist_map)
     for t, n in ((grad_output, "grad_output"), (grad_value, "grad_value"),
                  (grad_value_dpt_dist, "grad_value_dpt_dist"), (grad_sampling_loc, "grad_sampling_loc"),
                  (grad_attn_weight, "grad_attn_weight")):
-        _chk(t, n, _F32)
+        _chk(t, n, F)
     _same_device(value, grad_output, grad_value, grad_value_dpt_dist, grad_sampling_loc,
                  grad_attn_weight)
     if grad_output.numel() != B * Q * H * C or grad_value.shape != value.shape \
@@ -352,7 +372,7 @@ def dfa3d_fused_backward(value, value_dpt_dist, value_spatial_shapes, value_leve
         raise RuntimeError("inconsistent shapes in dfa3d_fused_backward")
     _step_check(B, im2col_step)
     with torch.cuda.device(value.device):
-        _lib.call("dfa3d_fused_backward", pr, _ptr(value), _ptr(value_dpt_dist),
+        _lib.call("dfa3d_fused_backward" + sfx, pr, _ptr(value), _ptr(value_dpt_dist),
                   _ptr(value_spatial_shapes), _ptr(value_level_start_index),
                   _ptr(sampling_locations), _ptr(attention_weights), _ptr(grad_output),
                   _ptr(grad_value), _ptr(grad_value_dpt_dist), _ptr(grad_sampling_loc),

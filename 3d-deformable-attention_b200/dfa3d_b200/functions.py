@@ -23,6 +23,11 @@ from torch.autograd.function import Function, once_differentiable
 from . import ext as ext_module
 
 
+def _grad_dtype(t):
+    """Gradients are float32 (also for bfloat16 storage) unless the call is in double precision."""
+    return torch.float64 if t.dtype == torch.float64 else torch.float32
+
+
 class MultiScaleDepthScoreSampleFunction(Function):
     @staticmethod
     def forward(ctx, value, value_spatial_shapes, value_level_start_index, sampling_locations,
@@ -40,7 +45,7 @@ class MultiScaleDepthScoreSampleFunction(Function):
     @once_differentiable
     def backward(ctx, grad_output):
         value, shapes, lsi, loc = ctx.saved_tensors
-        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_value = torch.zeros(value.shape, dtype=_grad_dtype(value), device=value.device)
         grad_sampling_loc = torch.empty_like(loc)     # every element is written by the kernel
         ext_module.ms_depth_score_sample_backward(
             value, shapes, lsi, loc, grad_output.contiguous(), grad_value, grad_sampling_loc,
@@ -66,7 +71,7 @@ class WeightedMultiScaleDeformableAttnFunction(Function):
     @once_differentiable
     def backward(ctx, grad_output):
         value, shapes, lsi, loc, attn, depth_score = ctx.saved_tensors
-        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
+        grad_value = torch.zeros(value.shape, dtype=_grad_dtype(value), device=value.device)
         grad_sampling_loc = torch.empty_like(loc)
         grad_attn_weight = torch.empty_like(attn)
         grad_depth_score = torch.empty_like(depth_score)
@@ -108,8 +113,8 @@ class MultiScale3DDeformableAttnFunction(Function):
         value, dist, shapes, lsi, loc, attn = ctx.saved_tensors
         if grad_output is None:
             return (None,) * 9
-        grad_value = torch.zeros(value.shape, dtype=torch.float32, device=value.device)
-        grad_dist = torch.zeros(dist.shape, dtype=torch.float32, device=dist.device)
+        grad_value = torch.zeros(value.shape, dtype=_grad_dtype(value), device=value.device)
+        grad_dist = torch.zeros(dist.shape, dtype=_grad_dtype(value), device=dist.device)
         grad_sampling_loc = torch.empty_like(loc)
         grad_attn_weight = torch.empty_like(attn)
         ext_module.dfa3d_fused_backward(

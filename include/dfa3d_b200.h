@@ -36,6 +36,7 @@ extern "C" {
 
 #define DFA3D_DTYPE_F32 0
 #define DFA3D_DTYPE_BF16 1
+#define DFA3D_DTYPE_F64 2 /* the *_f64 entry points only: every floating-point tensor is double */
 
 #define DFA3D_ACT_SOFTMAX 0 /* dfa3d_dist_from_logits: softmax over the D channels */
 #define DFA3D_ACT_SIGMOID 1 /* element-wise sigmoid */
@@ -260,6 +261,37 @@ int dfa3d_dist_from_logits_backward(const float *logits, int32_t B, int32_t D, i
                                     const int64_t *level_start, int32_t L, int32_t N,
                                     int32_t activation, const float *grad_dist, float *grad_logits,
                                     void *stream);
+
+/* Double precision.  The reference instantiates its kernels for float and double
+ * (AT_DISPATCH_FLOATING_TYPES, DFA3D/dfa3D/ops/csrc/cuda/wms_deform_attn_cuda.cu:267,344 and
+ * cuda/ms_depth_score_sample_cuda.cu:94,184).  The *_f64 entry points are the double instantiations of
+ * the entry points of the same name: every floating-point tensor -- value, dist, locations, attention
+ * weights, depth scores, outputs, all gradients -- is double, p->value_dtype and p->dist_dtype are
+ * DFA3D_DTYPE_F64, dist is (B,N,H,D) or (B,N,D) (no single-map option).  Accumulated gradients are
+ * caller-zeroed, the others overwritten, as in single precision.  These kernels are written for
+ * gradient checks and reference-grade comparisons, not for speed. */
+int dfa3d_depth_score_forward_f64(const dfa3d_problem *p, const double *dist, const int64_t *shapes3,
+                                  const int64_t *level_start, const double *loc3, double *depth_score,
+                                  void *stream);
+int dfa3d_depth_score_backward_f64(const dfa3d_problem *p, const double *dist, const int64_t *shapes3,
+                                   const int64_t *level_start, const double *loc3,
+                                   const double *grad_depth_score, double *grad_dist, double *grad_loc3,
+                                   void *stream);
+int dfa3d_wms_attn_forward_f64(const dfa3d_problem *p, const double *value, const int64_t *shapes2,
+                               const int64_t *level_start, const double *loc2, const double *attn,
+                               const double *depth_score, double *out, void *stream);
+int dfa3d_wms_attn_backward_f64(const dfa3d_problem *p, const double *value, const int64_t *shapes2,
+                                const int64_t *level_start, const double *loc2, const double *attn,
+                                const double *depth_score, const double *grad_out, double *grad_value,
+                                double *grad_loc2, double *grad_attn, double *grad_depth_score,
+                                void *stream);
+int dfa3d_fused_forward_f64(const dfa3d_problem *p, const double *value, const double *dist,
+                            const int64_t *shapes3, const int64_t *level_start, const double *loc3,
+                            const double *attn, double *out, double *depth_score_out, void *stream);
+int dfa3d_fused_backward_f64(const dfa3d_problem *p, const double *value, const double *dist,
+                             const int64_t *shapes3, const int64_t *level_start, const double *loc3,
+                             const double *attn, const double *grad_out, double *grad_value,
+                             double *grad_dist, double *grad_loc3, double *grad_attn, void *stream);
 
 #ifdef __cplusplus
 }

@@ -77,6 +77,11 @@ def test_validation_returns_codes_not_crashes(lib_built):
         if name.endswith("_ragged"):     # the offset table is required even for an empty problem
             assert getattr(lib, name)(ctypes.byref(empty), *([None] * n)) == -1, name
             assert getattr(lib, name)(ctypes.byref(empty), 16, *([None] * (n - 1))) == 0, name
+        elif name.endswith("_f64"):      # the double entry points want DFA3D_DTYPE_F64 in the descriptor
+            assert getattr(lib, name)(ctypes.byref(empty), *([None] * n)) == -1, name
+            assert b"F64" in lib.dfa3d_last_error()
+            empty64 = _lib.Problem(0, 4, 1, 4, 2, 1, 0, 1, _lib.DTYPE_F64, _lib.DTYPE_F64, 2)
+            assert getattr(lib, name)(ctypes.byref(empty64), *([None] * n)) == 0, name
         else:
             assert getattr(lib, name)(ctypes.byref(empty), *([None] * n)) == 0, name
     for name, n in _lib.ENTRY_POINTS_WITH_ANCHORS.items():
