@@ -129,7 +129,7 @@ def cpu_baseline(w, budget_cameras=1):
                          n["grad_out"], depth_score=ds)
         reps += 1
         el = time.perf_counter() - t0
-        if el > 10.0 or reps >= 5:
+        if el > 10.0 or (reps >= 5 and el > 2.0):      # a bounded sample: 2-10 s on all host threads
             break
     assert np.isfinite(out).all()
     cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
