@@ -421,6 +421,18 @@ def test_host_pipeline_matches_device_path(M):
         assert torch.equal(host_out["grad_loc"], gl.cpu()) and torch.equal(host_out["grad_attn"], ga.cpu())
         assert_close("grad_value", host_out["grad_value"], gv, **BWD)     # atomics: order may differ
         assert_close("grad_dist", host_out["grad_dist"], gd, **BWD)
+    # consecutive batches overlapping (join=False), joined once at the end; and the copies-only mode
+    for v in host_out.values():
+        v.fill_(float("nan"))
+    for i in range(3):
+        pipe.run(host_in, host_out, join=(i == 2))
+    torch.cuda.synchronize()
+    assert torch.equal(host_out["out"], out.cpu()) and torch.equal(host_out["grad_loc"], gl.cpu())
+    assert_close("grad_value", host_out["grad_value"], gv, **BWD)
+    pipe.run(host_in, host_out, join=False)
+    pipe.join()
+    torch.cuda.synchronize()
+    assert torch.equal(host_out["grad_attn"], ga.cpu())
     with pytest.raises(RuntimeError, match="pinned"):
         pipe.run({k: v.clone() for k, v in d.items()}, host_out)
 
