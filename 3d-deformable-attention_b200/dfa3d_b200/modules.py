@@ -9,6 +9,8 @@
 
   * ``TemporalSelfAttention`` -- the BEV self-attention over the previous and the current BEV
     (…/modules/temporal_self_attention.py:26-272), the caller of the plain 2-D operator.
+  * ``CustomMSDeformableAttention`` -- the detection decoder's cross-attention from object queries to
+    the BEV (…/modules/decoder.py:133-345), the other caller of the 2-D operator.
   * ``point_sampling`` -- the projection of the pillar reference points into the cameras that yields
     ``reference_points_cam`` and ``bev_mask`` (…/modules/encoder.py:421-476).
 
@@ -382,6 +384,81 @@ class SCAEncoderLayer(nn.Module):
     def forward(self, query, **kw):
         query = self.norm1(self.cross_attn(query, **kw))
         return self.norm2(query + self.ffn(query))
+
+
+class CustomMSDeformableAttention(nn.Module):
+    """Object queries attend to the BEV features with 2-D multi-scale deformable attention
+    (decoder.py:133-345; parameters and initialisation :200-227).  batch_first=False by default, like
+    the reference: query (Q, bs, E), value (N, bs, E)."""
+
+    def __init__(self, embed_dims=256, num_heads=8, num_levels=4, num_points=4, im2col_step=64, dropout=0.1,
+                 batch_first=False):
+        super().__init__()
+        if embed_dims % num_heads != 0:
+            raise ValueError(f"embed_dims must be divisible by num_heads, but got {embed_dims} and "
+                             f"{num_heads}")
+        self.embed_dims, self.num_heads = embed_dims, num_heads
+        self.num_levels, self.num_points = num_levels, num_points
+        self.im2col_step, self.batch_first = im2col_step, batch_first
+        self.dropout = nn.Dropout(dropout)
+        self.sampling_offsets = nn.Linear(embed_dims, num_heads * num_levels * num_points * 2)
+        self.attention_weights = nn.Linear(embed_dims, num_heads * num_levels * num_points)
+        self.value_proj = nn.Linear(embed_dims, embed_dims)
+        self.output_proj = nn.Linear(embed_dims, embed_dims)
+        self.init_weights()
+
+    def init_weights(self):
+        H, L, P = self.num_heads, self.num_levels, self.num_points
+        nn.init.zeros_(self.sampling_offsets.weight)
+        thetas = torch.arange(H, dtype=torch.float32) * (2.0 * math.pi / H)
+        grid = torch.stack([thetas.cos(), thetas.sin()], -1)
+        grid = (grid / grid.abs().max(-1, keepdim=True)[0]).view(H, 1, 1, 2).repeat(1, L, P, 1)
+        grid = grid * torch.arange(1, P + 1, dtype=torch.float32).view(1, 1, P, 1)
+        with torch.no_grad():
+            self.sampling_offsets.bias.copy_(grid.view(-1))
+            nn.init.zeros_(self.attention_weights.weight)
+            nn.init.zeros_(self.attention_weights.bias)
+            nn.init.xavier_uniform_(self.value_proj.weight)
+            nn.init.zeros_(self.value_proj.bias)
+            nn.init.xavier_uniform_(self.output_proj.weight)
+            nn.init.zeros_(self.output_proj.bias)
+
+    def forward(self, query, key=None, value=None, identity=None, query_pos=None, key_padding_mask=None,
+                reference_points=None, spatial_shapes=None, level_start_index=None):
+        """reference_points (bs, Q, L, 2) normalised positions, or (bs, Q, L, 4) boxes (cx, cy, w, h).
+        Returns dropout(output_proj(attention)) + identity, in the layout of `query`  -- :231-345."""
+        if value is None:
+            value = query
+        if identity is None:
+            identity = query
+        if query_pos is not None:
+            query = query + query_pos
+        if not self.batch_first:
+            query, value = query.permute(1, 0, 2), value.permute(1, 0, 2)
+        bs, Q, _ = query.shape
+        N = value.shape[1]
+        H, L, P = self.num_heads, self.num_levels, self.num_points
+        value = self.value_proj(value)
+        if key_padding_mask is not None:
+            value = value.masked_fill(key_padding_mask[..., None], 0.0)
+        value = value.view(bs, N, H, -1)
+        offsets = self.sampling_offsets(query).view(bs, Q, H, L, P, 2)
+        attn = self.attention_weights(query).view(bs, Q, H, L * P).softmax(-1).view(bs, Q, H, L, P)
+        if reference_points.shape[-1] == 2:
+            normalizer = torch.stack([spatial_shapes[..., 1], spatial_shapes[..., 0]], -1).to(offsets.dtype)
+            loc = reference_points[:, :, None, :, None, :] + offsets / normalizer[None, None, None, :, None, :]
+        elif reference_points.shape[-1] == 4:
+            loc = reference_points[:, :, None, :, None, :2] \
+                + offsets / P * reference_points[:, :, None, :, None, 2:] * 0.5
+        else:
+            raise ValueError("Last dim of reference_points must be 2 or 4, but get "
+                             f"{reference_points.shape[-1]} instead.")
+        out = MultiScaleDeformableAttnFunction_fp32.apply(value.contiguous(), spatial_shapes, level_start_index,
+                                                          loc.contiguous(), attn.contiguous(), self.im2col_step)
+        out = self.output_proj(out)
+        if not self.batch_first:
+            out = out.permute(1, 0, 2)
+        return self.dropout(out) + identity
 
 
 class BEVFormerEncoderLayer(nn.Module):

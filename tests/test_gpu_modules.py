@@ -415,3 +415,42 @@ def test_full_encoder_layer_is_the_composition_of_its_blocks(lib_built):
     assert torch.isfinite(q.grad).all() and q.grad.abs().sum() > 0
     for n, p in layer.named_parameters():
         assert p.grad is not None and torch.isfinite(p.grad).all(), n
+
+
+@pytest.mark.parametrize("ref_dim", [2, 4])
+def test_decoder_attention_matches_grid_sample_form(lib_built, monkeypatch, ref_dim):
+    """CustomMSDeformableAttention (object queries -> BEV, decoder.py:231-345), with point and with box
+    reference points, against the same module on the 4-D grid_sample operator."""
+    E, H, L, P, bs, Q = 32, 4, 2, 4, 2, 37
+    levels = ((8, 10), (4, 5))
+    N = sum(h * w for h, w in levels)
+    g = torch.Generator().manual_seed(33)
+    query = torch.randn(Q, bs, E, generator=g).to(DEV)
+    pos = torch.randn(Q, bs, E, generator=g).to(DEV)
+    bev = torch.randn(N, bs, E, generator=g).to(DEV)
+    refp = torch.rand(bs, Q, L, ref_dim, generator=g).to(DEV)
+    shapes = torch.tensor(levels, dtype=torch.int64, device=DEV)
+    lsi = torch.tensor([0, levels[0][0] * levels[0][1]], dtype=torch.int64, device=DEV)
+
+    def run():
+        torch.manual_seed(9)
+        m = modules.CustomMSDeformableAttention(embed_dims=E, num_heads=H, num_levels=L, num_points=P,
+                                                dropout=0.0).to(DEV)
+        with torch.no_grad():
+            m.sampling_offsets.weight.normal_(0, 0.05)
+            m.attention_weights.weight.normal_(0, 0.05)
+        q = query.clone().requires_grad_(True)
+        v = bev.clone().requires_grad_(True)
+        out = m(q, value=v, query_pos=pos, reference_points=refp, spatial_shapes=shapes, level_start_index=lsi)
+        assert out.shape == q.shape
+        out.pow(2).sum().backward()
+        return out.detach(), q.grad.clone(), v.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()}
+
+    got = run()
+    monkeypatch.setattr(modules, "MultiScaleDeformableAttnFunction_fp32", _MsdaGridSampleOp)
+    want = run()
+    torch.testing.assert_close(got[0], want[0], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(got[1], want[1], rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(got[2], want[2], rtol=1e-3, atol=1e-4)
+    for n in want[3]:
+        torch.testing.assert_close(got[3][n], want[3][n], rtol=1e-3, atol=1e-4, msg=lambda m_, n=n: f"{n}: {m_}")
