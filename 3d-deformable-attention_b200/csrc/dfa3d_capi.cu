@@ -39,15 +39,20 @@ int check_problem(const dfa3d_problem *p, bool need_value, bool need_dist) {
   if (need_value) {
     if (p->C <= 0 || p->C > DFA3D_MAX_CHANNELS)
       return fail(DFA3D_ERR_UNSUPPORTED, "C=%d outside [1, %d]", p->C, DFA3D_MAX_CHANNELS);
-    if (p->value_dtype != DFA3D_DTYPE_F32 && p->value_dtype != DFA3D_DTYPE_BF16)
+    if (p->value_dtype != DFA3D_DTYPE_F32 && p->value_dtype != DFA3D_DTYPE_BF16 &&
+        p->value_dtype != DFA3D_DTYPE_F16)
       return fail(DFA3D_ERR_INVALID_ARGUMENT, "value_dtype %d is not a DFA3D_DTYPE_*", p->value_dtype);
     if ((long long)p->N * p->H * p->C >= (1LL << 31))
       return fail(DFA3D_ERR_UNSUPPORTED, "N*H*C must stay below 2^31 (one camera's value slice)");
   }
   if (need_dist) {
     if (p->D <= 0) return fail(DFA3D_ERR_INVALID_ARGUMENT, "D must be positive (got %d)", p->D);
-    if (p->dist_dtype != DFA3D_DTYPE_F32 && p->dist_dtype != DFA3D_DTYPE_BF16)
+    if (p->dist_dtype != DFA3D_DTYPE_F32 && p->dist_dtype != DFA3D_DTYPE_BF16 &&
+        p->dist_dtype != DFA3D_DTYPE_F16)
       return fail(DFA3D_ERR_INVALID_ARGUMENT, "dist_dtype %d is not a DFA3D_DTYPE_*", p->dist_dtype);
+    if (need_value && (p->value_dtype == DFA3D_DTYPE_F16) != (p->dist_dtype == DFA3D_DTYPE_F16))
+      return fail(DFA3D_ERR_UNSUPPORTED, "fp16 storage: value and dist must both be DFA3D_DTYPE_F16 "
+                  "(got value_dtype %d, dist_dtype %d)", p->value_dtype, p->dist_dtype);
     if (p->dist_head_stride != 0 && p->dist_head_stride != p->D)
       return fail(DFA3D_ERR_INVALID_ARGUMENT, "dist_head_stride must be 0 (shared) or D (per head), got %lld",
                   (long long)p->dist_head_stride);
@@ -109,7 +114,7 @@ int dfa3d_depth_score_forward(const dfa3d_problem *p, const void *dist, const in
   REQUIRE_PTR(depth_score); REQUIRE_ALIGNED(depth_score);
   dfa3d::KArgs a = base_args(p, 3, 3);
   a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3; a.ds_out = depth_score;
-  return finish(dfa3d::launch_depth_score_forward(a, p->dist_dtype == DFA3D_DTYPE_BF16,
+  return finish(dfa3d::launch_depth_score_forward(a, p->dist_dtype,
                                                   (cudaStream_t)stream),
                 "dfa3d_depth_score_forward launch");
 }
@@ -126,7 +131,7 @@ int dfa3d_depth_score_backward(const dfa3d_problem *p, const void *dist, const i
   dfa3d::KArgs a = base_args(p, 3, 3);
   a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
   a.grad_ds_in = grad_depth_score; a.grad_dist = grad_dist; a.grad_loc = grad_loc3;
-  return finish(dfa3d::launch_depth_score_backward(a, p->dist_dtype == DFA3D_DTYPE_BF16,
+  return finish(dfa3d::launch_depth_score_backward(a, p->dist_dtype,
                                                    (cudaStream_t)stream),
                 "dfa3d_depth_score_backward launch");
 }
@@ -142,7 +147,7 @@ int dfa3d_wms_attn_forward(const dfa3d_problem *p, const void *value, const int6
   dfa3d::KArgs a = base_args(p, 2, 2);
   a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn;
   a.ds_in = depth_score; a.out = out;
-  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16, false,
+  return finish(dfa3d::launch_forward(a, p->value_dtype, DFA3D_DTYPE_F32,
                                       dfa3d::kGivenDepthScore, (cudaStream_t)stream),
                 "dfa3d_wms_attn_forward launch");
 }
@@ -163,7 +168,7 @@ int dfa3d_wms_attn_backward(const dfa3d_problem *p, const void *value, const int
   a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn;
   a.ds_in = depth_score; a.grad_out = grad_out; a.grad_value = grad_value; a.grad_loc = grad_loc2;
   a.grad_attn = grad_attn; a.grad_ds_out = grad_depth_score;
-  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16, false,
+  return finish(dfa3d::launch_backward(a, p->value_dtype, DFA3D_DTYPE_F32,
                                        dfa3d::kGivenDepthScore, (cudaStream_t)stream),
                 "dfa3d_wms_attn_backward launch");
 }
@@ -180,8 +185,8 @@ static int fused_forward_impl(const dfa3d_problem *p, const int32_t *query_offse
   dfa3d::KArgs a = base_args(p, 3, 3);
   a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
   a.attn = attn; a.out = out; a.ds_out = depth_score_out; a.q_off = query_offsets;
-  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16,
-                                      p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kFused,
+  return finish(dfa3d::launch_forward(a, p->value_dtype,
+                                      p->dist_dtype, dfa3d::kFused,
                                       (cudaStream_t)stream),
                 "dfa3d_fused_forward launch");
 }
@@ -217,8 +222,8 @@ static int fused_backward_impl(const dfa3d_problem *p, const int32_t *query_offs
   a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.loc = loc3;
   a.attn = attn; a.grad_out = grad_out; a.grad_value = grad_value; a.grad_dist = grad_dist;
   a.grad_loc = grad_loc3; a.grad_attn = grad_attn; a.q_off = query_offsets;
-  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16,
-                                       p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kFused,
+  return finish(dfa3d::launch_backward(a, p->value_dtype,
+                                       p->dist_dtype, dfa3d::kFused,
                                        (cudaStream_t)stream),
                 "dfa3d_fused_backward launch");
 }
@@ -251,7 +256,7 @@ int dfa3d_msda_forward(const dfa3d_problem *p, const void *value, const int64_t 
   REQUIRE_ALIGNED(value); REQUIRE_ALIGNED(out);
   dfa3d::KArgs a = base_args(p, 2, 2);
   a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn; a.out = out;
-  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16, false,
+  return finish(dfa3d::launch_forward(a, p->value_dtype, DFA3D_DTYPE_F32,
                                       dfa3d::kGivenDepthScore, (cudaStream_t)stream),
                 "dfa3d_msda_forward launch");
 }
@@ -269,7 +274,7 @@ int dfa3d_msda_backward(const dfa3d_problem *p, const void *value, const int64_t
   dfa3d::KArgs a = base_args(p, 2, 2);
   a.value = value; a.shapes = shapes2; a.lsi = level_start; a.loc = loc2; a.attn = attn;
   a.grad_out = grad_out; a.grad_value = grad_value; a.grad_loc = grad_loc2; a.grad_attn = grad_attn;
-  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16, false,
+  return finish(dfa3d::launch_backward(a, p->value_dtype, DFA3D_DTYPE_F32,
                                        dfa3d::kGivenDepthScore, (cudaStream_t)stream),
                 "dfa3d_msda_backward launch");
 }
@@ -293,8 +298,8 @@ static int attn3d_forward_impl(const dfa3d_problem *p, int32_t num_anchors,
   a.value = value; a.dist = dist; a.shapes = shapes3; a.lsi = level_start; a.ref = ref_points;
   a.off_uv = offsets_uv; a.off_d = offsets_depth; a.logits = logits; a.Z = num_anchors; a.out = out;
   a.q_off = query_offsets;
-  return finish(dfa3d::launch_forward(a, p->value_dtype == DFA3D_DTYPE_BF16,
-                                      p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kCallerFused,
+  return finish(dfa3d::launch_forward(a, p->value_dtype,
+                                      p->dist_dtype, dfa3d::kCallerFused,
                                       (cudaStream_t)stream),
                 "dfa3d_attn3d_forward launch");
 }
@@ -341,8 +346,8 @@ static int attn3d_backward_impl(const dfa3d_problem *p, int32_t num_anchors,
   a.grad_out = grad_out; a.grad_value = grad_value; a.grad_dist = grad_dist;
   a.grad_off_uv = grad_offsets_uv; a.grad_off_d = grad_offsets_depth; a.grad_logits = grad_logits;
   a.q_off = query_offsets;
-  return finish(dfa3d::launch_backward(a, p->value_dtype == DFA3D_DTYPE_BF16,
-                                       p->dist_dtype == DFA3D_DTYPE_BF16, dfa3d::kCallerFused,
+  return finish(dfa3d::launch_backward(a, p->value_dtype,
+                                       p->dist_dtype, dfa3d::kCallerFused,
                                        (cudaStream_t)stream),
                 "dfa3d_attn3d_backward launch");
 }
@@ -444,12 +449,12 @@ int dfa3d_dist_from_logits(const float *logits, int32_t B, int32_t D, int32_t ma
                            const int64_t *level_start, int32_t L, int32_t N, int32_t activation,
                            int32_t dist_dtype, void *dist, void *stream) {
   if (int rc = check_producer(B, D, map_h, map_w, shape_stride, L, N, activation)) return rc;
-  if (dist_dtype != DFA3D_DTYPE_F32 && dist_dtype != DFA3D_DTYPE_BF16)
+  if (dist_dtype != DFA3D_DTYPE_F32 && dist_dtype != DFA3D_DTYPE_BF16 && dist_dtype != DFA3D_DTYPE_F16)
     return fail(DFA3D_ERR_INVALID_ARGUMENT, "dist_dtype %d is not a DFA3D_DTYPE_*", dist_dtype);
   if (B == 0 || N == 0) return DFA3D_OK;
   REQUIRE_PTR(logits); REQUIRE_PTR(spatial_shapes); REQUIRE_PTR(level_start); REQUIRE_PTR(dist);
   return finish(dfa3d::launch_dist_from_logits(logits, spatial_shapes, shape_stride, level_start, dist,
-                                               dist_dtype == DFA3D_DTYPE_BF16, B, D, map_h, map_w, N, L,
+                                               dist_dtype, B, D, map_h, map_w, N, L,
                                                activation == DFA3D_ACT_SIGMOID, (cudaStream_t)stream),
                 "dfa3d_dist_from_logits launch");
 }

@@ -14,6 +14,7 @@
 //   corner k          : 0=(y0,x0) 1=(y0,x1) 2=(y1,x1) 3=(y1,x0);  in-image iff 0 <= y <= H-1, 0 <= x <= W-1
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -29,6 +30,8 @@ constexpr int kMaxLevels = 32;
 //                     assembly and softmax (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/
 //                     spatial_cross_attention.py:498-538) happen in the prologue; depth scores from dist
 enum Mode { kFused = 0, kGivenDepthScore = 1, kCallerFused = 2 };
+// Storage type codes = DFA3D_DTYPE_F32 / _BF16 / _F16 of the C header.
+enum StorageType { kDtypeF32 = 0, kDtypeBF16 = 1, kDtypeF16 = 3 };
 __host__ __device__ constexpr bool mode_has_depth(int m) { return m != kGivenDepthScore; }
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
@@ -63,8 +66,8 @@ constexpr int kThreads = kWarpsPerCta * 32;
 
 // Kernel argument block (device pointers + sizes).  Unused pointers are null.
 struct KArgs {
-  const void *value;       // (B,N,H,C) fp32|bf16
-  const void *dist;        // (B,N,H,D) or (B,N,D) fp32|bf16
+  const void *value;       // (B,N,H,C) fp32|bf16|fp16
+  const void *dist;        // (B,N,H,D) or (B,N,D) fp32|bf16|fp16
   const int64_t *shapes;   // (L, shape_stride) int64
   const int64_t *lsi;      // (L) int64
   const float *loc;        // (B,Q,H,L,P,loc_stride)
@@ -294,6 +297,12 @@ __device__ __forceinline__ float load_scalar(const float *p) { return __ldg(p); 
 __device__ __forceinline__ float load_scalar(const __nv_bfloat16 *p) {
   return __bfloat162float(__ldg(p));
 }
+__device__ __forceinline__ float load_scalar(const __half *p) { return __half2float(__ldg(p)); }
+
+// Two packed fp16 values (low half first) widened to fp32.
+__device__ __forceinline__ float2 widen_half2(uint32_t bits) {
+  return __half22float2(*reinterpret_cast<const __half2 *>(&bits));
+}
 
 // One gathered row: where it starts and what it is multiplied by.
 struct __align__(8) RowEntry {
@@ -327,6 +336,15 @@ __device__ __forceinline__ void load_pair(const __nv_bfloat16 *p, float &lo, flo
   if ((reinterpret_cast<uintptr_t>(p) & 3) == 0) {
     const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(p));
     lo = __uint_as_float(t << 16); hi = __uint_as_float(t & 0xffff0000u);
+  } else {
+    lo = load_scalar(p); hi = load_scalar(p + 1);
+  }
+}
+
+__device__ __forceinline__ void load_pair(const __half *p, float &lo, float &hi) {
+  if ((reinterpret_cast<uintptr_t>(p) & 3) == 0) {
+    const float2 t = widen_half2(__ldg(reinterpret_cast<const uint32_t *>(p)));
+    lo = t.x; hi = t.y;
   } else {
     lo = load_scalar(p); hi = load_scalar(p + 1);
   }
@@ -370,7 +388,20 @@ template <> struct RowVec<__nv_bfloat16> {
   }
 };
 
-// Backward: 4 channels per lane for both storage types, so that the lane-to-channel mapping, the
+template <> struct RowVec<__half> {
+  static constexpr int kElems = 8;
+  __device__ static __forceinline__ void load(const __half *p, float (&v)[8]) {
+    const uint4 t = __ldg(reinterpret_cast<const uint4 *>(p));
+    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = widen_half2(u[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+};
+
+// Backward: 4 channels per lane for every storage type, so that the lane-to-channel mapping, the
 // register footprint and the one 16-byte vector reduction per lane are those of fp32 rows (measured:
 // with 8 bf16 per lane the backward needs 80+ registers and runs 30 % slower than the fp32 one).
 template <typename VT> struct RowVec4 : RowVec<VT> {};
@@ -382,6 +413,15 @@ template <> struct RowVec4<__nv_bfloat16> {
     v[1] = __uint_as_float(t.x & 0xffff0000u);
     v[2] = __uint_as_float(t.y << 16);
     v[3] = __uint_as_float(t.y & 0xffff0000u);
+  }
+};
+
+template <> struct RowVec4<__half> {
+  static constexpr int kElems = 4;
+  __device__ static __forceinline__ void load(const __half *p, float (&v)[4]) {
+    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(p));
+    const float2 a = widen_half2(t.x), b = widen_half2(t.y);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
   }
 };
 

@@ -6,12 +6,13 @@
 // F.interpolate(mode="nearest") per feature level (:273-276), flatten + permute + cat of the levels
 // (…/modules/transformer.py:368-391) and the permute to (bs*cams, sum hw, D) of the spatial
 // cross-attention (spatial_cross_attention.py:727-728).  Here one kernel reads the logits once and
-// writes dist (B, N, D) -- fp32 or bf16 -- for all levels, channel-last; its backward reads the
+// writes dist (B, N, D) -- fp32, bf16 or fp16 -- for all levels, channel-last; its backward reads the
 // gradient of that tensor and the logits once and writes the gradient of the logits.
 //
 // Nearest resize, as torch computes it: source index = min(floor(dst * scale), size - 1) with
 // scale = (float)source size / (float)level size.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 #include "dfa3d_b200.h"
@@ -28,7 +29,7 @@ struct ProdArgs {
   const float *logits;      // (B, D, hs, ws)
   const int64_t *shapes;    // (L, shape_stride) int64: (h, w, ...) per level
   const int64_t *lsi;       // (L) int64
-  void *dist;               // (B, N, D) fp32 | bf16
+  void *dist;               // (B, N, D) fp32 | bf16 | fp16
   const float *grad_dist;   // (B, N, D) fp32
   float *grad_logits;       // (B, D, hs, ws)
   int B, D, hs, ws, N, L, shape_stride;
@@ -41,6 +42,7 @@ __device__ __forceinline__ int nearest_src(int dst, float scale, int size) {
 
 __device__ __forceinline__ void store_bin(float *p, float v) { *p = v; }
 __device__ __forceinline__ void store_bin(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void store_bin(__half *p, float v) { *p = __float2half_rn(v); }
 
 // Forward: a CTA owns kTile consecutive rows n of one camera.  The logits of their source pixels are
 // staged transposed in shared memory (loads run along the map's x axis: coalesced where the level has
@@ -181,7 +183,7 @@ dist_from_logits_backward_kernel(const ProdArgs a) {
 int dist_producer_max_bins() { return kMaxBins; }
 
 cudaError_t launch_dist_from_logits(const float *logits, const int64_t *shapes, int shape_stride,
-                                    const int64_t *lsi, void *dist, bool dist_bf16, int B, int D, int hs,
+                                    const int64_t *lsi, void *dist, int dist_dtype, int B, int D, int hs,
                                     int ws, int N, int L, bool sigmoid, cudaStream_t s) {
   if (B == 0 || N == 0) return cudaSuccess;
   ProdArgs a{};
@@ -191,9 +193,10 @@ cudaError_t launch_dist_from_logits(const float *logits, const int64_t *shapes, 
   for (int b0 = 0; b0 < B; b0 += 65535) {
     ProdArgs c = a;
     c.logits = logits + (long long)b0 * D * hs * ws;
-    c.dist = static_cast<char *>(dist) + (long long)b0 * N * D * (dist_bf16 ? 2 : 4);
+    c.dist = static_cast<char *>(dist) + (long long)b0 * N * D * (dist_dtype == 0 ? 4 : 2);
     const dim3 grid((unsigned)((N + kTile - 1) / kTile), (unsigned)min(65535, B - b0), 1);
-    if (dist_bf16) dist_from_logits_kernel<__nv_bfloat16><<<grid, kProdThreads, 0, s>>>(c);
+    if (dist_dtype == 3) dist_from_logits_kernel<__half><<<grid, kProdThreads, 0, s>>>(c);
+    else if (dist_dtype == 1) dist_from_logits_kernel<__nv_bfloat16><<<grid, kProdThreads, 0, s>>>(c);
     else dist_from_logits_kernel<float><<<grid, kProdThreads, 0, s>>>(c);
   }
   return cudaGetLastError();

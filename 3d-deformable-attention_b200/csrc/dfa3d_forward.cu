@@ -283,30 +283,35 @@ static cudaError_t launch_forward_vd(const KArgs &a0, cudaStream_t s) {
   return cudaSuccess;
 }
 
+// Storage types are the DFA3D_DTYPE_* codes of the C header.  fp32 and bf16 combine freely; fp16 value
+// goes with fp16 dist (what a half-precision caller passes) -- the C entry points reject the rest.
 template <int MODE>
-static cudaError_t launch_forward_m(const KArgs &a, bool value_bf16, bool dist_bf16, cudaStream_t s) {
-  if (value_bf16)
-    return dist_bf16 ? launch_forward_vd<__nv_bfloat16, __nv_bfloat16, MODE>(a, s)
-                     : launch_forward_vd<__nv_bfloat16, float, MODE>(a, s);
-  return dist_bf16 ? launch_forward_vd<float, __nv_bfloat16, MODE>(a, s)
-                   : launch_forward_vd<float, float, MODE>(a, s);
+static cudaError_t launch_forward_m(const KArgs &a, int value_dtype, int dist_dtype, cudaStream_t s) {
+  if (value_dtype == kDtypeF16) return launch_forward_vd<__half, __half, MODE>(a, s);
+  if (value_dtype == kDtypeBF16)
+    return dist_dtype == kDtypeBF16 ? launch_forward_vd<__nv_bfloat16, __nv_bfloat16, MODE>(a, s)
+                                    : launch_forward_vd<__nv_bfloat16, float, MODE>(a, s);
+  return dist_dtype == kDtypeBF16 ? launch_forward_vd<float, __nv_bfloat16, MODE>(a, s)
+                                  : launch_forward_vd<float, float, MODE>(a, s);
 }
 
-cudaError_t launch_forward(const KArgs &a, bool value_bf16, bool dist_bf16, int mode, cudaStream_t s) {
+cudaError_t launch_forward(const KArgs &a, int value_dtype, int dist_dtype, int mode, cudaStream_t s) {
   if (a.items == 0) return cudaSuccess;
   if (mode == kGivenDepthScore) {   // dist is not read: its type parameter is irrelevant
-    return value_bf16 ? launch_forward_vd<__nv_bfloat16, float, kGivenDepthScore>(a, s)
-                      : launch_forward_vd<float, float, kGivenDepthScore>(a, s);
+    if (value_dtype == kDtypeF16) return launch_forward_vd<__half, float, kGivenDepthScore>(a, s);
+    return value_dtype == kDtypeBF16 ? launch_forward_vd<__nv_bfloat16, float, kGivenDepthScore>(a, s)
+                                     : launch_forward_vd<float, float, kGivenDepthScore>(a, s);
   }
-  if (mode == kCallerFused) return launch_forward_m<kCallerFused>(a, value_bf16, dist_bf16, s);
-  return launch_forward_m<kFused>(a, value_bf16, dist_bf16, s);
+  if (mode == kCallerFused) return launch_forward_m<kCallerFused>(a, value_dtype, dist_dtype, s);
+  return launch_forward_m<kFused>(a, value_dtype, dist_dtype, s);
 }
 
-cudaError_t launch_depth_score_forward(const KArgs &a, bool dist_bf16, cudaStream_t s) {
+cudaError_t launch_depth_score_forward(const KArgs &a, int dist_dtype, cudaStream_t s) {
   const long long npts = a.items * a.LP;
   if (npts == 0) return cudaSuccess;
   const unsigned grid = (unsigned)min((npts + kThreads - 1) / kThreads, (long long)148 * 64);
-  if (dist_bf16) dfa3d_depth_score_forward_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(a);
+  if (dist_dtype == kDtypeF16) dfa3d_depth_score_forward_kernel<__half><<<grid, kThreads, 0, s>>>(a);
+  else if (dist_dtype == kDtypeBF16) dfa3d_depth_score_forward_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(a);
   else dfa3d_depth_score_forward_kernel<float><<<grid, kThreads, 0, s>>>(a);
   return cudaGetLastError();
 }

@@ -7,10 +7,10 @@ struct dfa3d_problem;
 namespace dfa3d {
 struct KArgs;
 // mode: dfa3d::Mode
-cudaError_t launch_forward(const KArgs &a, bool value_bf16, bool dist_bf16, int mode, cudaStream_t s);
-cudaError_t launch_depth_score_forward(const KArgs &a, bool dist_bf16, cudaStream_t s);
-cudaError_t launch_backward(const KArgs &a, bool value_bf16, bool dist_bf16, int mode, cudaStream_t s);
-cudaError_t launch_depth_score_backward(const KArgs &a, bool dist_bf16, cudaStream_t s);
+cudaError_t launch_forward(const KArgs &a, int value_dtype, int dist_dtype, int mode, cudaStream_t s);
+cudaError_t launch_depth_score_forward(const KArgs &a, int dist_dtype, cudaStream_t s);
+cudaError_t launch_backward(const KArgs &a, int value_dtype, int dist_dtype, int mode, cudaStream_t s);
+cudaError_t launch_depth_score_backward(const KArgs &a, int dist_dtype, cudaStream_t s);
 // per-camera re-batching (dfa3d_rebatch.cu)
 cudaError_t launch_rebatch_plan(const uint8_t *mask, int cams, int bs, int Q, int Z, int32_t *counts,
                                 int32_t *offsets, int32_t *op_offsets, int32_t *packed_query,
@@ -43,8 +43,9 @@ cudaError_t launch_depth_backward64(const dfa3d_problem *p, const double *dist, 
                                     double *grad_dist, double *grad_loc3, cudaStream_t s);
 // depth-distribution producer (dfa3d_dist_producer.cu)
 int dist_producer_max_bins();
+// dist_dtype: DFA3D_DTYPE_F32 (0), _BF16 (1) or _F16 (3)
 cudaError_t launch_dist_from_logits(const float *logits, const int64_t *shapes, int shape_stride,
-                                    const int64_t *lsi, void *dist, bool dist_bf16, int B, int D, int hs,
+                                    const int64_t *lsi, void *dist, int dist_dtype, int B, int D, int hs,
                                     int ws, int N, int L, bool sigmoid, cudaStream_t s);
 cudaError_t launch_dist_from_logits_backward(const float *logits, const int64_t *shapes, int shape_stride,
                                              const int64_t *lsi, const float *grad_dist,

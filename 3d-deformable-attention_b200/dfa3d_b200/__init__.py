@@ -12,11 +12,15 @@ from .functions import (  # noqa: F401
     DeformableAttn3DFromOffsetsFunction_fp32,
     MultiScale3DDeformableAttnFunction,
     MultiScaleDeformableAttnFunction,
+    MultiScaleDeformableAttnFunction_fp16,
     MultiScaleDeformableAttnFunction_fp32,
+    MultiScale3DDeformableAttnFunction_fp16,
     MultiScale3DDeformableAttnFunction_fp32,
     MultiScaleDepthScoreSampleFunction,
+    MultiScaleDepthScoreSampleFunction_fp16,
     MultiScaleDepthScoreSampleFunction_fp32,
     WeightedMultiScaleDeformableAttnFunction,
+    WeightedMultiScaleDeformableAttnFunction_fp16,
     WeightedMultiScaleDeformableAttnFunction_fp32,
 )
 
@@ -28,4 +32,6 @@ __all__ = [
     "MultiScale3DDeformableAttnFunction_fp32",
     "DeformableAttn3DFromOffsetsFunction", "DeformableAttn3DFromOffsetsFunction_fp32",
     "MultiScaleDeformableAttnFunction", "MultiScaleDeformableAttnFunction_fp32",
+    "MultiScaleDepthScoreSampleFunction_fp16", "WeightedMultiScaleDeformableAttnFunction_fp16",
+    "MultiScale3DDeformableAttnFunction_fp16", "MultiScaleDeformableAttnFunction_fp16",
 ]

@@ -13,6 +13,7 @@ ABI_VERSION = 2
 DTYPE_F32 = 0
 DTYPE_BF16 = 1
 DTYPE_F64 = 2
+DTYPE_F16 = 3
 MAX_LEVELS = 32
 MAX_CHANNELS = 1024
 

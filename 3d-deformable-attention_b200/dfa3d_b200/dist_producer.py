@@ -30,6 +30,9 @@ def _check(logits, shapes, lsi):
     return logits.contiguous(), shapes.contiguous(), lsi.contiguous()
 
 
+_DTYPES = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16}
+
+
 class DepthDistributionFunction(Function):
     @staticmethod
     def forward(ctx, logits, spatial_shapes, level_start_index, num_pixels, activation="softmax",
@@ -39,15 +42,15 @@ class DepthDistributionFunction(Function):
         logits, shapes, lsi = _check(logits, spatial_shapes, level_start_index)
         if activation not in ("softmax", "sigmoid"):
             raise ValueError("activation must be 'softmax' or 'sigmoid'")
-        if dtype not in (torch.float32, torch.bfloat16):
-            raise ValueError("dtype must be torch.float32 or torch.bfloat16")
+        if dtype not in _DTYPES:
+            raise ValueError("dtype must be torch.float32, torch.bfloat16 or torch.float16")
         B, D, h, w = logits.shape
         act = _lib.ACT_SOFTMAX if activation == "softmax" else _lib.ACT_SIGMOID
         dist = torch.empty((B, int(num_pixels), D), dtype=dtype, device=logits.device)
         with torch.cuda.device(logits.device):
             _lib.call_plain("dfa3d_dist_from_logits", logits.data_ptr(), B, D, h, w, shapes.data_ptr(),
                             shapes.shape[1], lsi.data_ptr(), shapes.shape[0], int(num_pixels), act,
-                            _lib.DTYPE_BF16 if dtype == torch.bfloat16 else _lib.DTYPE_F32,
+                            _DTYPES[dtype],
                             dist.data_ptr(), _stream(logits))
         ctx.save_for_backward(logits, shapes, lsi)
         ctx.act, ctx.N = act, int(num_pixels)

@@ -42,13 +42,15 @@ def _step_check(batch, im2col_step):
 
 _F32 = (torch.float32,)
 _F64 = (torch.float64,)
-_VAL = (torch.float32, torch.bfloat16)
+_VAL = (torch.float32, torch.bfloat16, torch.float16)
 _I64 = (torch.int64,)
 
 
 def _dt(t):
     if t.dtype == torch.float64:
         return _lib.DTYPE_F64
+    if t.dtype == torch.float16:
+        return _lib.DTYPE_F16
     return _lib.DTYPE_BF16 if t.dtype == torch.bfloat16 else _lib.DTYPE_F32
 
 

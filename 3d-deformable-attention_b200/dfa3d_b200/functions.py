@@ -12,6 +12,13 @@
   * `_fp32` aliases cast inputs to float32 under autocast like the reference's
     ``custom_fwd(cast_inputs=torch.float32)`` variants.
 
+  * `_fp16` aliases are the reference's ``custom_fwd(cast_inputs=torch.float16)`` variants
+    (…attn_function.py:24,183,353; multi_scale_deformable_attn_function.py:15), which the reference's
+    modules pick when ``value`` is half (spatial_cross_attention.py:556-560).  The reference's kernels are
+    instantiated for float and double only, so there those classes stop with "not implemented for
+    'Half'"; here value / value_dpt_dist stay half in memory and are read as such by the kernels, the small
+    tensors are widened to float32, arithmetic is float32 and the outputs come back as half.
+
 Differences, all additive: ``value_dpt_dist`` may also be (B,N,D), shared by all heads (the reference
 needs it repeated per head); ``value`` / ``value_dpt_dist`` may be bfloat16; the one-stage Function
 takes an optional trailing ``return_depth_score`` flag; the one-stage backward is a single kernel
@@ -24,7 +31,7 @@ from . import ext as ext_module
 
 
 def _grad_dtype(t):
-    """Gradients are float32 (also for bfloat16 storage) unless the call is in double precision."""
+    """Gradients are float32 (also for bfloat16 / float16 storage) unless the call is in double precision."""
     return torch.float64 if t.dtype == torch.float64 else torch.float32
 
 
@@ -289,3 +296,45 @@ MultiScale3DDeformableAttnRaggedFunction_fp32 = _fp32_variant(
     MultiScale3DDeformableAttnRaggedFunction, "MultiScale3DDeformableAttnRaggedFunction_fp32")
 DeformableAttn3DFromOffsetsRaggedFunction_fp32 = _fp32_variant(
     DeformableAttn3DFromOffsetsRaggedFunction, "DeformableAttn3DFromOffsetsRaggedFunction_fp32")
+
+
+def _fp16_variant(cls, name, storage):
+    """Half-precision variant of `cls`.  `storage` = positions of the tensors that stay half for the kernels
+    (value, value_dpt_dist); every other half tensor is widened to float32 first, and when any argument was
+    half the outputs are returned as half.  Gradients are computed in float32; autograd casts them to the
+    dtype of the inputs they belong to."""
+
+    def forward(ctx, *args):
+        args = list(args)
+        half = any(torch.is_tensor(a) and a.dtype == torch.float16 for a in args)
+        for i, a in enumerate(args):
+            if not torch.is_tensor(a) or not a.is_floating_point():
+                continue
+            if i in storage:
+                args[i] = a.half() if half else a       # value and dist share one storage type
+            elif a.dtype == torch.float16:
+                args[i] = a.float()
+        out = cls.forward(ctx, *args)
+        if not half:
+            return out
+        if torch.is_tensor(out):
+            return out.half()
+        return tuple(o.half() if torch.is_tensor(o) else o for o in out)
+
+    def backward(ctx, *grads):
+        return cls.backward(ctx, *[g.float() if torch.is_tensor(g) and g.dtype == torch.float16 else g
+                                   for g in grads])
+
+    fwd = torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float16)(forward)
+    bwd = torch.amp.custom_bwd(device_type="cuda")(backward)
+    return type(name, (Function,), {"forward": staticmethod(fwd), "backward": staticmethod(bwd)})
+
+
+MultiScaleDepthScoreSampleFunction_fp16 = _fp16_variant(
+    MultiScaleDepthScoreSampleFunction, "MultiScaleDepthScoreSampleFunction_fp16", (0,))
+WeightedMultiScaleDeformableAttnFunction_fp16 = _fp16_variant(
+    WeightedMultiScaleDeformableAttnFunction, "WeightedMultiScaleDeformableAttnFunction_fp16", (0,))
+MultiScale3DDeformableAttnFunction_fp16 = _fp16_variant(
+    MultiScale3DDeformableAttnFunction, "MultiScale3DDeformableAttnFunction_fp16", (0, 1))
+MultiScaleDeformableAttnFunction_fp16 = _fp16_variant(
+    MultiScaleDeformableAttnFunction, "MultiScaleDeformableAttnFunction_fp16", (0,))

@@ -25,7 +25,7 @@ class Workload:
     C: int = 32                              # channels per head
     seed: int = 0
     oob: bool = False                        # ~15 % of points with x or y outside [0,1]
-    value_dtype: str = "fp32"                # "fp32" | "bf16" (value and dist storage)
+    value_dtype: str = "fp32"                # "fp32" | "bf16" | "fp16" (value and dist storage)
     local: bool = False                      # locations clustered around per-query reference points
 
     @property
@@ -49,7 +49,7 @@ class Workload:
     def algorithmic_bytes(self):
         """Compulsory HBM traffic (forward, backward): every input read once, every output written
         once, dist counted un-repeated (B,N,D), depth_score not materialised, no memset traffic."""
-        e = 2 if self.value_dtype == "bf16" else 4
+        e = 2 if self.value_dtype in ("bf16", "fp16") else 4
         pts = self.points
         value = self.B * self.N * self.H * self.C
         dist = self.B * self.N * self.D
@@ -96,8 +96,8 @@ def make_inputs(w: Workload, seed=None, head_repeat=False):
 
     value ~ N(0,1); dist = softmax over D of N(0,1); x,y ~ U(0,1) (or U(-0.0423,1.0423): each axis in
     range with probability 0.922, so ~15 % of points leave the image); z ~ U(0,1);
-    attn = softmax over L*P of N(0,1); grad_out ~ N(0,1).  With value_dtype == "bf16", value and dist
-    are rounded to bf16 once (and returned as fp32 holding the rounded values)."""
+    attn = softmax over L*P of N(0,1); grad_out ~ N(0,1).  With value_dtype == "bf16" / "fp16", value and dist
+    are rounded to that type once (and returned as fp32 holding the rounded values)."""
     g = torch.Generator().manual_seed(w.seed if seed is None else seed)
     value = torch.randn(w.B, w.N, w.H, w.C, generator=g)
     dist = torch.randn(w.B, w.N, w.D, generator=g).softmax(-1)
@@ -120,6 +120,9 @@ def make_inputs(w: Workload, seed=None, head_repeat=False):
     if w.value_dtype == "bf16":
         value = value.bfloat16().float()
         dist = dist.bfloat16().float()
+    elif w.value_dtype == "fp16":
+        value = value.half().float()
+        dist = dist.half().float()
     if head_repeat:
         dist = dist.view(w.B, w.N, 1, w.D).repeat(1, 1, w.H, 1)
     shapes, lsi = level_tensors(w)

@@ -7,8 +7,8 @@
  * the message of the calling thread's last failure.
  *
  * Tensor layouts are the reference's (all contiguous, row-major):
- *   value        (B, N, H, C)           fp32 or bf16        N = sum over levels of h_l * w_l
- *   dist         (B, N, H, D) or (B, N, D) shared by all heads   fp32 or bf16, per-pixel depth distribution
+ *   value        (B, N, H, C)           fp32, bf16 or fp16  N = sum over levels of h_l * w_l
+ *   dist         (B, N, H, D) or (B, N, D) shared by all heads   fp32, bf16 or fp16, per-pixel depth distribution
  *   loc3 / loc2  (B, Q, H, L, P, 3|2)   fp32   (x, y[, z]) in units of the level's width/height/depth
  *   attn         (B, Q, H, L, P)        fp32
  *   depth_score  (B, Q, H, L, P, 4)     fp32   corner order 0=(y0,x0) 1=(y0,x1) 2=(y1,x1) 3=(y1,x0)
@@ -37,6 +37,8 @@ extern "C" {
 #define DFA3D_DTYPE_F32 0
 #define DFA3D_DTYPE_BF16 1
 #define DFA3D_DTYPE_F64 2 /* the *_f64 entry points only: every floating-point tensor is double */
+#define DFA3D_DTYPE_F16 3 /* IEEE half storage of value and dist together (what the reference's *_fp16
+                             Functions pass); arithmetic, the other tensors and all gradients stay fp32 */
 
 #define DFA3D_ACT_SOFTMAX 0 /* dfa3d_dist_from_logits: softmax over the D channels */
 #define DFA3D_ACT_SIGMOID 1 /* element-wise sigmoid */
@@ -51,7 +53,7 @@ typedef struct dfa3d_problem {
   int32_t N;  /* pixels over all levels */
   int32_t H;  /* heads */
   int32_t C;  /* channels per head, any value up to DFA3D_MAX_CHANNELS.  Vectorised kernels: fp32 value
-                 C in {8,16,32,64}; bf16 value C in {16,32,64,128} forward and {8,16,32,64} backward.
+                 C in {8,16,32,64}; bf16 / fp16 value C in {16,32,64,128} forward and {8,16,32,64} backward.
                  Every other width (fp32 C = 128 and bf16 C = 128 in the backward included) runs a
                  lane-strided kernel with the same results, several times slower. */
   int32_t D;  /* depth bins = channel count of dist */
@@ -240,7 +242,7 @@ int dfa3d_rebatch_combine(const float *src, const int32_t *row_of, const int32_t
                           void *stream);
 
 /* Producer of `dist`: the depth network's logits (B, D, map_h, map_w) fp32 become the operator's
- * dist (B, N, D), fp32 or bf16, in one pass: softmax over D (or sigmoid), nearest-neighbour resize to
+ * dist (B, N, D), fp32, bf16 or fp16, in one pass: softmax over D (or sigmoid), nearest-neighbour resize to
  * every level (spatial_shapes (L, shape_stride) / level_start (L), int64, device), channel-last layout.
  * Replaces BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/dense_heads/depth_head.py:265-276
  * (feat_dpt.softmax(1) | sigmoid(); F.interpolate(dpt_dist, size=scale, mode="nearest") per level) and

@@ -106,7 +106,13 @@ def test_validation_returns_codes_not_crashes(lib_built):
     assert prod(None, 1, 257, 4, 4, None, 2, None, 1, 16, 0, 0, None, None) == -2 and b"256" in lib.dfa3d_last_error()
     assert prod(None, 1, 64, 4, 4, None, 2, None, 1, 16, 5, 0, None, None) == -1 and b"activation" in lib.dfa3d_last_error()
     assert prod(None, 1, 64, 4, 4, None, 4, None, 1, 16, 0, 0, None, None) == -1 and b"shape_stride" in lib.dfa3d_last_error()
-    assert prod(None, 1, 64, 4, 4, None, 2, None, 1, 16, 0, 3, None, None) == -1 and b"dist_dtype" in lib.dfa3d_last_error()
+    assert prod(None, 1, 64, 4, 4, None, 2, None, 1, 16, 0, 2, None, None) == -1 and b"dist_dtype" in lib.dfa3d_last_error()
+    assert prod(None, 1, 64, 4, 4, None, 2, None, 1, 16, 0, _lib.DTYPE_F16, None, None) == -1 and b"logits" in lib.dfa3d_last_error()
+    # half storage: value and dist together
+    bad = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, _lib.DTYPE_F16, 0, 2)
+    assert lib.dfa3d_fused_forward(ctypes.byref(bad), *([None] * 9)) == -2 and b"fp16" in lib.dfa3d_last_error()
+    half = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, _lib.DTYPE_F16, _lib.DTYPE_F16, 2)
+    assert lib.dfa3d_fused_forward(ctypes.byref(half), *([None] * 9)) == -1 and b"null" in lib.dfa3d_last_error()
     assert lib.dfa3d_dist_from_logits_backward(None, 1, 64, 0, 4, None, 2, None, 1, 16, 0, None, None, None) == -1
     # a dist map needs both of its sizes
     bad = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, 0, 0, 2, 3, 0)

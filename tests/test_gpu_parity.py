@@ -32,7 +32,7 @@ def REF():
         pytest.skip(f"reference op not available: {e}")
 
 
-def run_fused(M, d, shared_dist, bf16=False, fn=None):
+def run_fused(M, d, shared_dist, bf16=False, fn=None, storage=torch.bfloat16):
     """One-stage Function forward + backward on the GPU.  d: CPU dict with head-repeated dist."""
     fn = fn or M.MultiScale3DDeformableAttnFunction
     value, dist = d["value"], d["dist"]
@@ -44,7 +44,7 @@ def run_fused(M, d, shared_dist, bf16=False, fn=None):
     shapes, lsi, go = d["shapes"].to(DEV), d["lsi"].to(DEV), d["grad_out"].to(DEV)
     if bf16:   # bf16 storage: gradients for value/dist are taken through the low-level entry points
         from dfa3d_b200 import ext
-        vb, db = value.bfloat16(), dist.bfloat16()
+        vb, db = value.to(storage), dist.to(storage)
         out, ds = ext.dfa3d_fused_forward(vb, db, shapes, lsi, loc.detach(), attn.detach(), 64)
         gv = torch.zeros_like(value); gd = torch.zeros_like(dist)
         gl = torch.empty_like(loc); ga = torch.empty_like(attn)
@@ -114,6 +114,78 @@ def test_bf16_storage_matches_oracle(M, case):
         got = run_fused(M, d, shared, bf16=True)
         check_against(got, ref, shared)
         check_against(got, ref, shared, fwd=BF16, bwd=BF16)
+
+
+@pytest.mark.parametrize("case", ["C16", "C32", "C64", "C128", "C24_generic"])
+def test_fp16_storage_matches_oracle(M, case):
+    """IEEE half value/dist (what the reference's *_fp16 Functions hand to the extension), fp32 arithmetic
+    and gradients: the oracle consumes the same half-rounded numbers in fp32 and the fp32-level tolerance is
+    asserted."""
+    C = int(case[1:].split("_")[0])
+    w = wl.WORKLOADS["odd"].with_(name=case, C=C, H=2 if C == 128 else 8, value_dtype="fp16", seed=8)
+    d = wl.make_inputs(w, head_repeat=True)
+    ref = oracle_all(d, np.float32)
+    for shared in (False, True):
+        check_against(run_fused(M, d, shared, bf16=True, storage=torch.float16), ref, shared)
+
+
+def test_fp16_functions_like_the_reference_variants(M):
+    """The *_fp16 Function variants (…attn_function.py:24,183,353) with half tensors throughout, as the
+    reference's modules call them when value is half: outputs are half, equal to the fp32 oracle on the
+    half-rounded inputs up to the output rounding; gradients arrive in the dtype of their inputs.  One-stage
+    and two-stage."""
+    w = wl.WORKLOADS["odd"].with_(C=32, seed=41)
+    d = wl.make_inputs(w, head_repeat=True)
+    h = {k: (v.half() if v.is_floating_point() else v) for k, v in d.items()}
+    ref = oracle_all({k: (v.float() if v.is_floating_point() else v) for k, v in h.items()}, np.float32)
+    shapes, lsi, go = d["shapes"].to(DEV), d["lsi"].to(DEV), h["grad_out"].to(DEV)
+    HALF = dict(rtol=2e-3, atol=0.0, atol_frac=1e-3)        # half an ulp of fp16 = 2^-11
+
+    def leaves():
+        return [h[k].to(DEV).requires_grad_(True) for k in ("value", "dist", "loc", "attn")]
+
+    value, dist, loc, attn = leaves()
+    out, ds = M.MultiScale3DDeformableAttnFunction_fp16.apply(value, dist, shapes, lsi, loc, attn, 64)
+    assert out.dtype == torch.float16 and ds.dtype == torch.float16
+    out.backward(go)
+    got1 = dict(out=out, ds=ds, grad_value=value.grad, grad_dist=dist.grad, grad_loc=loc.grad, grad_attn=attn.grad)
+    value, dist, loc, attn = leaves()
+    ds2 = M.MultiScaleDepthScoreSampleFunction_fp16.apply(dist, shapes, lsi, loc, 64)
+    out2 = M.WeightedMultiScaleDeformableAttnFunction_fp16.apply(
+        value, shapes[:, :2].contiguous(), lsi, loc[..., :2].contiguous(), attn, ds2, 64)
+    assert out2.dtype == torch.float16 and ds2.dtype == torch.float16
+    out2.backward(go)
+    got2 = dict(out=out2, ds=ds2, grad_value=value.grad, grad_dist=dist.grad, grad_loc=loc.grad,
+                grad_attn=attn.grad)
+    for tag, got, tol in (("one-stage", got1, HALF), ("two-stage", got2, dict(rtol=8e-3, atol=0.0, atol_frac=4e-3))):
+        for k in ("grad_value", "grad_dist", "grad_loc", "grad_attn"):
+            assert got[k].dtype == torch.float16, (tag, k)
+        # the two-stage path rounds depth_score to half between its stages
+        for k in ("out", "ds", "grad_value", "grad_dist", "grad_attn"):
+            assert_close(f"{tag}/{k}", got[k].float(), ref[k], **tol)
+
+
+def test_fp16_functions_under_autocast(M):
+    """Under autocast the *_fp16 variants cast float32 inputs to half themselves (custom_fwd cast_inputs), the
+    *_fp32 ones cast half inputs to float32."""
+    d = wl.make_inputs(wl.WORKLOADS["tiny"], head_repeat=True)
+    t = {k: v.to(DEV) for k, v in d.items()}
+    with torch.autocast("cuda", dtype=torch.float16):
+        out16, _ = M.MultiScale3DDeformableAttnFunction_fp16.apply(t["value"], t["dist"], t["shapes"], t["lsi"],
+                                                                   t["loc"], t["attn"], 64)
+        out32, _ = M.MultiScale3DDeformableAttnFunction_fp32.apply(t["value"].half(), t["dist"].half(),
+                                                                   t["shapes"], t["lsi"], t["loc"], t["attn"], 64)
+    assert out16.dtype == torch.float16 and out32.dtype == torch.float32
+    assert_close("autocast", out16.float(), out32, rtol=2e-2, atol=0.0, atol_frac=1e-2)
+
+
+def test_fp16_needs_value_and_dist_in_half_together(M):
+    from dfa3d_b200 import ext
+    t = {k: v.to(DEV) for k, v in wl.make_inputs(wl.WORKLOADS["tiny"]).items()}
+    with pytest.raises(RuntimeError, match="fp16 storage"):
+        ext.dfa3d_fused_forward(t["value"].half(), t["dist"], t["shapes"], t["lsi"], t["loc"], t["attn"], 64)
+    with pytest.raises(RuntimeError, match="fp16 storage"):
+        ext.dfa3d_fused_forward(t["value"], t["dist"].half(), t["shapes"], t["lsi"], t["loc"], t["attn"], 64)
 
 
 def test_two_stage_api_matches_oracle(M):
