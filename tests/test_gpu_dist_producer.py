@@ -58,6 +58,10 @@ def test_producer_matches_softmax_and_nearest_resize(lib_built, case, activation
     assert got16.dtype == torch.bfloat16
     diff = (got16.float() - want.detach().bfloat16().float()).abs()
     assert (diff <= want.detach().abs() * 2 ** -7).all()          # at most one bf16 ulp apart
+    goth = depth_distribution(logits.detach(), shapes, lsi, N, activation=activation, dtype=torch.float16)
+    assert goth.dtype == torch.float16
+    diff = (goth.float() - want.detach().half().float()).abs()
+    assert (diff <= want.detach().abs() * 2 ** -10 + 2 ** -24).all()   # one fp16 ulp (subnormal step 2^-24)
     assert (diff > 0).float().mean() < 1e-3
 
 
