@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "dfa3d_b200", "libdfa3d_b200.so")
 SOURCES = ["dfa3d_forward.cu", "dfa3d_backward.cu", "dfa3d_rebatch.cu", "dfa3d_dist_producer.cu",
-           "dfa3d_fp64.cu", "dfa3d_capi.cu"]
+           "dfa3d_fp64.cu", "dfa3d_layer_ops.cu", "dfa3d_capi.cu"]
 RATES_SRC = os.path.join(CSRC, "rates", "dfa3d_rates.cu")
 RATES_OUT = os.path.join(HERE, "dfa3d_b200", "libdfa3d_rates.so")
 INCLUDE = os.path.join(HERE, "..", "include")

@@ -475,6 +475,55 @@ int dfa3d_dist_from_logits_backward(const float *logits, int32_t B, int32_t D, i
                 "dfa3d_dist_from_logits_backward launch");
 }
 
+// ---- encoder-layer row operations --------------------------------------------------------------
+static int check_rows(int64_t rows, int32_t E) {
+  if (rows < 0) return fail(DFA3D_ERR_INVALID_ARGUMENT, "rows must be >= 0 (got %lld)", (long long)rows);
+  if (E <= 0) return fail(DFA3D_ERR_INVALID_ARGUMENT, "E must be positive (got %d)", E);
+  if (E % 4 != 0 || E > dfa3d::layer_norm_max_columns())
+    return fail(DFA3D_ERR_UNSUPPORTED, "E=%d: rows of a multiple of 4 columns up to %d are covered", E,
+                dfa3d::layer_norm_max_columns());
+  return DFA3D_OK;
+}
+
+int dfa3d_add_layer_norm_forward(const float *x, const float *residual, const float *gamma,
+                                 const float *beta, int64_t rows, int32_t E, float eps, float *sum_out,
+                                 float *y, float *mean, float *rstd, void *stream) {
+  if (int rc = check_rows(rows, E)) return rc;
+  if (!(eps >= 0.f)) return fail(DFA3D_ERR_INVALID_ARGUMENT, "eps must be >= 0");
+  if ((residual == nullptr) != (sum_out == nullptr))
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "residual and sum_out must be given together or not at all");
+  if (rows == 0) return DFA3D_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(gamma); REQUIRE_PTR(beta); REQUIRE_PTR(y); REQUIRE_PTR(mean); REQUIRE_PTR(rstd);
+  REQUIRE_ALIGNED(x); REQUIRE_ALIGNED(residual); REQUIRE_ALIGNED(gamma); REQUIRE_ALIGNED(beta);
+  REQUIRE_ALIGNED(sum_out); REQUIRE_ALIGNED(y);
+  return finish(dfa3d::launch_add_layer_norm_forward(x, residual, gamma, beta, rows, E, eps, sum_out, y, mean,
+                                                     rstd, (cudaStream_t)stream),
+                "dfa3d_add_layer_norm_forward launch");
+}
+
+int dfa3d_layer_norm_backward(const float *grad_y, const float *in, const float *gamma,
+                              const float *mean, const float *rstd, int64_t rows, int32_t E,
+                              float *grad_in, float *grad_gamma, float *grad_beta, void *stream) {
+  if (int rc = check_rows(rows, E)) return rc;
+  if (rows == 0) return DFA3D_OK;
+  REQUIRE_PTR(grad_y); REQUIRE_PTR(in); REQUIRE_PTR(gamma); REQUIRE_PTR(mean); REQUIRE_PTR(rstd);
+  REQUIRE_PTR(grad_in); REQUIRE_PTR(grad_gamma); REQUIRE_PTR(grad_beta);
+  REQUIRE_ALIGNED(grad_y); REQUIRE_ALIGNED(in); REQUIRE_ALIGNED(gamma); REQUIRE_ALIGNED(grad_in);
+  return finish(dfa3d::launch_layer_norm_backward(grad_y, in, gamma, mean, rstd, rows, E, grad_in, grad_gamma,
+                                                  grad_beta, (cudaStream_t)stream),
+                "dfa3d_layer_norm_backward launch");
+}
+
+int dfa3d_column_sum(const float *src, int64_t rows, int32_t cols, float *dst, void *stream) {
+  if (rows < 0 || cols < 0)
+    return fail(DFA3D_ERR_INVALID_ARGUMENT, "rows and cols must be >= 0 (got %lld, %d)", (long long)rows, cols);
+  if (cols % 4 != 0) return fail(DFA3D_ERR_UNSUPPORTED, "cols=%d must be a multiple of 4", cols);
+  if (rows == 0 || cols == 0) return DFA3D_OK;
+  REQUIRE_PTR(src); REQUIRE_PTR(dst);
+  REQUIRE_ALIGNED(src);
+  return finish(dfa3d::launch_column_sum(src, rows, cols, dst, (cudaStream_t)stream), "dfa3d_column_sum launch");
+}
+
 // ---- double precision -------------------------------------------------------------------------
 // Same checks as check_problem(); both dtype fields must say DFA3D_DTYPE_F64 and dist must be laid out
 // like value (no single-map option in double).

@@ -51,4 +51,15 @@ cudaError_t launch_dist_from_logits_backward(const float *logits, const int64_t 
                                              const int64_t *lsi, const float *grad_dist,
                                              float *grad_logits, int B, int D, int hs, int ws, int N,
                                              int L, bool sigmoid, cudaStream_t s);
+// encoder-layer row operations (dfa3d_layer_ops.cu); E = columns of a row, a multiple of 4 up to 1024
+int layer_norm_max_columns();
+cudaError_t launch_add_layer_norm_forward(const float *x, const float *residual, const float *gamma,
+                                          const float *beta, long long rows, int E, float eps,
+                                          float *sum_out, float *y, float *mean, float *rstd,
+                                          cudaStream_t s);
+cudaError_t launch_layer_norm_backward(const float *grad_y, const float *in, const float *gamma,
+                                       const float *mean, const float *rstd, long long rows, int E,
+                                       float *grad_in, float *grad_gamma, float *grad_beta,
+                                       cudaStream_t s);
+cudaError_t launch_column_sum(const float *src, long long rows, int cols, float *dst, cudaStream_t s);
 }  // namespace dfa3d

@@ -74,10 +74,14 @@ PLAIN_ENTRY_POINTS = {
                               + [_I32] * 4 + [ctypes.c_void_p] * 2,
     "dfa3d_dist_from_logits_backward": [ctypes.c_void_p] + [_I32] * 4 + [ctypes.c_void_p, _I32, ctypes.c_void_p]
                                        + [_I32] * 3 + [ctypes.c_void_p] * 3,
+    "dfa3d_add_layer_norm_forward": [ctypes.c_void_p] * 4 + [_I64, _I32, ctypes.c_float] + [ctypes.c_void_p] * 5,
+    "dfa3d_layer_norm_backward": [ctypes.c_void_p] * 5 + [_I64, _I32] + [ctypes.c_void_p] * 4,
+    "dfa3d_column_sum": [ctypes.c_void_p, _I64, _I32, ctypes.c_void_p, ctypes.c_void_p],
 }
 ACT_SOFTMAX, ACT_SIGMOID = 0, 1
 
 _lib = None
+calls = 0      # successful entry-point calls so far (each launches at least one kernel)
 
 
 def load():
@@ -120,6 +124,8 @@ def call_plain(name, *args):
     if rc != 0:
         msg = lib.dfa3d_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{name} failed ({ERROR_NAMES.get(rc, rc)}): {msg}")
+    global calls
+    calls += 1
 
 
 def call(name, problem, *ptrs):
@@ -129,3 +135,5 @@ def call(name, problem, *ptrs):
     if rc != 0:
         msg = lib.dfa3d_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{name} failed ({ERROR_NAMES.get(rc, rc)}): {msg}")
+    global calls
+    calls += 1

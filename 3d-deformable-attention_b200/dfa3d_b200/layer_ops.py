@@ -1,0 +1,136 @@
+"""Row operations of the encoder layer around the attention operator, on the library's own kernels
+(C entry points ``dfa3d_add_layer_norm_forward``, ``dfa3d_layer_norm_backward``, ``dfa3d_column_sum``).
+
+The reference's layer (BEVFormer_DFA3D/projects/mmdet3d_plugin/bevformer/modules/encoder.py:363-411,
+custom_base_transformer_layer.py) applies ``norm(x + branch(x))`` after each block with torch's LayerNorm
+and torch's Linear.  Here
+
+  * ``AddLayerNorm`` is a LayerNorm (same parameters, same state dict keys as ``torch.nn.LayerNorm``)
+    whose forward takes an optional residual: one kernel forms the sum and normalises it, one kernel
+    produces the input gradient and the weight / bias gradients.
+  * ``Linear`` is ``torch.nn.Linear`` whose bias gradient is a single column-sum kernel; the matrix
+    products stay with cuBLAS.
+
+float32 CUDA tensors only; like the rest of the package there is no fallback path.
+"""
+import torch
+import torch.nn as nn
+from torch.autograd.function import Function, once_differentiable
+
+from . import _lib
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check(t, name):
+    if not t.is_cuda or t.dtype != torch.float32:
+        raise RuntimeError(f"{name} must be a float32 CUDA tensor, got {t.dtype} on {t.device}")
+
+
+def column_sum(src):
+    """(rows, cols) float32 -> (cols,): sum over the rows."""
+    _check(src, "src")
+    if src.dim() != 2:
+        raise RuntimeError("column_sum takes a (rows, cols) matrix")
+    src = src.contiguous()
+    rows, cols = src.shape
+    dst = torch.zeros(cols, dtype=torch.float32, device=src.device)
+    with torch.cuda.device(src.device):
+        _lib.call_plain("dfa3d_column_sum", src.data_ptr(), rows, cols, dst.data_ptr(), _stream(src))
+    return dst
+
+
+class AddLayerNormFunction(Function):
+    @staticmethod
+    def forward(ctx, x, residual, weight, bias, eps):
+        """LayerNorm(x + residual) over the last dimension; residual may be None."""
+        for t, n in ((x, "x"), (weight, "weight"), (bias, "bias")):
+            _check(t, n)
+        E = x.shape[-1]
+        if weight.numel() != E or bias.numel() != E:
+            raise RuntimeError(f"weight and bias must have {E} elements")
+        x = x.contiguous()
+        rows = x.numel() // E if E else 0
+        summed = None
+        if residual is not None:
+            _check(residual, "residual")
+            if residual.shape != x.shape:
+                raise RuntimeError(f"residual {tuple(residual.shape)} does not match x {tuple(x.shape)}")
+            residual = residual.contiguous()
+            summed = torch.empty_like(x)
+        y = torch.empty_like(x)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        weight, bias = weight.contiguous(), bias.contiguous()
+        with torch.cuda.device(x.device):
+            _lib.call_plain("dfa3d_add_layer_norm_forward", x.data_ptr(),
+                            None if residual is None else residual.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                            rows, E, float(eps), None if summed is None else summed.data_ptr(), y.data_ptr(),
+                            mean.data_ptr(), rstd.data_ptr(), _stream(x))
+        ctx.save_for_backward(x if summed is None else summed, weight, mean, rstd)
+        ctx.has_residual = residual is not None
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_y):
+        inp, weight, mean, rstd = ctx.saved_tensors
+        E = inp.shape[-1]
+        grad_y = grad_y.contiguous()
+        grad_in = torch.empty_like(inp)
+        grad_w = torch.zeros(E, dtype=torch.float32, device=inp.device)
+        grad_b = torch.zeros(E, dtype=torch.float32, device=inp.device)
+        with torch.cuda.device(inp.device):
+            _lib.call_plain("dfa3d_layer_norm_backward", grad_y.data_ptr(), inp.data_ptr(), weight.data_ptr(),
+                            mean.data_ptr(), rstd.data_ptr(), mean.numel(), E, grad_in.data_ptr(),
+                            grad_w.data_ptr(), grad_b.data_ptr(), _stream(inp))
+        return grad_in, (grad_in if ctx.has_residual else None), grad_w, grad_b, None
+
+
+class AddLayerNorm(nn.LayerNorm):
+    """``torch.nn.LayerNorm`` over the last dimension with an optional residual: ``forward(x, residual)``
+    returns ``LayerNorm(x + residual)``."""
+
+    def __init__(self, normalized_shape, eps=1e-5):
+        super().__init__(normalized_shape, eps=eps, elementwise_affine=True)
+        if len(self.normalized_shape) != 1:
+            raise ValueError("AddLayerNorm normalises the last dimension only")
+
+    def forward(self, x, residual=None):
+        return AddLayerNormFunction.apply(x, residual, self.weight, self.bias, self.eps)
+
+
+class LinearFunction(Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        # written into a tensor of its own (F.linear returns a view of the 2-D product for inputs of more
+        # dimensions, which an in-place activation after a custom Function must not modify)
+        y = torch.empty(x.shape[:-1] + (weight.shape[0],), dtype=x.dtype, device=x.device)
+        torch.addmm(bias, x.reshape(-1, x.shape[-1]), weight.t(), out=y.view(-1, weight.shape[0]))
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_out):
+        x, weight = ctx.saved_tensors
+        g2 = grad_out.reshape(-1, grad_out.shape[-1])
+        grad_x = grad_w = grad_b = None
+        if ctx.needs_input_grad[0]:
+            grad_x = (g2 @ weight).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            grad_w = g2.t() @ x.reshape(-1, x.shape[-1])
+        if ctx.needs_input_grad[2]:
+            grad_b = column_sum(g2)
+        return grad_x, grad_w, grad_b
+
+
+class Linear(nn.Linear):
+    """``torch.nn.Linear`` (same parameters); the bias gradient is one column-sum kernel."""
+
+    def forward(self, x):
+        if self.bias is None or self.out_features % 4 != 0:
+            return super().forward(x)
+        return LinearFunction.apply(x, self.weight, self.bias)

@@ -20,6 +20,8 @@ the depth distribution is passed as (B, N, D) shared by all heads instead of bei
 (:497 in the reference); the per-camera re-batching keeps exactly the (camera, query) pairs that are
 visible, as packed rows moved by kernels (``rebatch.RebatchPlan``), instead of Python loops over tensors
 padded to the longest camera, and the operator is called once for all cameras with their row offsets.
+The layers' norms are ``layer_ops.AddLayerNorm`` (torch LayerNorm parameters; the residual add happens
+inside the norm kernel) and the projections ``layer_ops.Linear`` (bias gradient by a column-sum kernel).
 """
 import math
 
@@ -31,6 +33,7 @@ from .functions import (MultiScaleDeformableAttnFunction_fp32,
                         DeformableAttn3DFromOffsetsRaggedFunction_fp32,
                         MultiScale3DDeformableAttnFunction_fp32,
                         MultiScale3DDeformableAttnRaggedFunction_fp32)
+from .layer_ops import AddLayerNorm, Linear
 from .rebatch import (CombineCamerasFunction, GatherQueriesFunction, GatherSharedRowsFunction, RebatchPlan,
                       gather_per_camera)
 
@@ -128,10 +131,10 @@ class MSDeformableAttention3D_DFA3D(nn.Module):
         self.embed_dims, self.num_heads = embed_dims, num_heads
         self.num_levels, self.num_points = num_levels, num_points
         self.im2col_step, self.batch_first = im2col_step, batch_first
-        self.sampling_offsets = nn.Linear(embed_dims, num_heads * num_levels * num_points * 2)
-        self.sampling_offsets_depth = nn.Linear(embed_dims, num_heads * num_levels * num_points)
-        self.attention_weights = nn.Linear(embed_dims, num_heads * num_levels * num_points)
-        self.value_proj = nn.Linear(embed_dims, embed_dims)
+        self.sampling_offsets = Linear(embed_dims, num_heads * num_levels * num_points * 2)
+        self.sampling_offsets_depth = Linear(embed_dims, num_heads * num_levels * num_points)
+        self.attention_weights = Linear(embed_dims, num_heads * num_levels * num_points)
+        self.value_proj = Linear(embed_dims, embed_dims)
         self.init_weights()
 
     def init_weights(self):
@@ -231,7 +234,7 @@ class SpatialCrossAttention_DFA3D(nn.Module):
         self.deformable_attention = deformable_attention or MSDeformableAttention3D_DFA3D(embed_dims)
         if not use_empty:
             self.deformable_attention.compute_weight_update = False
-        self.output_proj = nn.Linear(embed_dims, embed_dims)
+        self.output_proj = Linear(embed_dims, embed_dims)
         self.dropout = nn.Dropout(dropout)
         if use_empty:
             self.empty_query = nn.Embedding(bev_h * bev_w * num_head, embed_dims)
@@ -240,14 +243,16 @@ class SpatialCrossAttention_DFA3D(nn.Module):
 
     def forward(self, query, key=None, value=None, value_dpt_dist=None, reference_points_cam=None,
                 bev_mask=None, spatial_shapes=None, level_start_index=None, residual=None,
-                query_pos=None, rebatch_plan=None, dist_map=None):
+                query_pos=None, rebatch_plan=None, dist_map=None, return_residual=False):
         """query (bs, Q, E); value (num_cams, N, bs, E) (`key` is accepted and, as in the reference,
         not used by the attention); value_dpt_dist (num_cams, N, bs, D);
         reference_points_cam (num_cams, bs, Q, Z, 3); bev_mask (num_cams, bs, Q, Z).
         ``rebatch_plan``: a ``RebatchPlan`` of this bev_mask built earlier (bev_mask is geometry: one
         plan serves every layer of a frame); without it the plan is built here, which reads the packed
         row count back from the device once.  ``dist_map=(h, w)``: value_dpt_dist is one h x w map per
-        camera, (num_cams, h*w, bs, D), read by all levels with nearest indexing.  Returns (bs, Q, E)."""
+        camera, (num_cams, h*w, bs, D), read by all levels with nearest indexing.  Returns (bs, Q, E);
+        with ``return_residual`` the two summands (attention branch, residual) separately, for a norm that
+        adds them itself."""
         inp_residual = query if residual is None else residual
         if query_pos is not None:
             query = query + query_pos
@@ -272,8 +277,8 @@ class SpatialCrossAttention_DFA3D(nn.Module):
                 self.empty_query.weight.view(self.bev_h * self.bev_w, self.num_head * E), plan)
             out_rows = out_rows + ((1 - update_weight) * empty.view(-1, self.num_head, E)).mean(-2)
         slots = CombineCamerasFunction.apply(out_rows, plan)                      # sum over cameras / count
-        slots = self.output_proj(slots)
-        return self.dropout(slots) + inp_residual
+        slots = self.dropout(self.output_proj(slots))
+        return (slots, inp_residual) if return_residual else slots + inp_residual
 
 
 class TemporalSelfAttention(nn.Module):
@@ -292,12 +297,12 @@ class TemporalSelfAttention(nn.Module):
         self.num_levels, self.num_points, self.num_bev_queue = num_levels, num_points, num_bev_queue
         self.im2col_step, self.batch_first = im2col_step, batch_first
         self.dropout = nn.Dropout(dropout)
-        self.sampling_offsets = nn.Linear(embed_dims * num_bev_queue,
+        self.sampling_offsets = Linear(embed_dims * num_bev_queue,
                                           num_bev_queue * num_heads * num_levels * num_points * 2)
-        self.attention_weights = nn.Linear(embed_dims * num_bev_queue,
+        self.attention_weights = Linear(embed_dims * num_bev_queue,
                                            num_bev_queue * num_heads * num_levels * num_points)
-        self.value_proj = nn.Linear(embed_dims, embed_dims)
-        self.output_proj = nn.Linear(embed_dims, embed_dims)
+        self.value_proj = Linear(embed_dims, embed_dims)
+        self.output_proj = Linear(embed_dims, embed_dims)
         self.init_weights()
 
     def init_weights(self):
@@ -317,11 +322,12 @@ class TemporalSelfAttention(nn.Module):
             nn.init.zeros_(self.output_proj.bias)
 
     def forward(self, query, key=None, value=None, identity=None, query_pos=None, key_padding_mask=None,
-                reference_points=None, spatial_shapes=None, level_start_index=None):
+                reference_points=None, spatial_shapes=None, level_start_index=None, return_residual=False):
         """query (bs, Q, E); value (bs*num_bev_queue, Q, E) = [previous BEV, current BEV] per batch
         element, or None (then the current queries stand for both, :180-184); reference_points
         (bs*num_bev_queue, Q, num_levels, 2); spatial_shapes (L, 2); level_start_index (L).
-        Returns (bs, Q, E)  -- :130-272."""
+        Returns (bs, Q, E)  -- :130-272; with ``return_residual`` the attention branch and the identity
+        separately."""
         if self.num_bev_queue != 2:
             raise ValueError("the BEV queue holds the previous and the current BEV: num_bev_queue == 2")
         if value is None:
@@ -363,7 +369,8 @@ class TemporalSelfAttention(nn.Module):
         out = self.output_proj(out)
         if not self.batch_first:
             out = out.permute(1, 0, 2)
-        return self.dropout(out) + identity
+        out = self.dropout(out)
+        return (out, identity) if return_residual else out + identity
 
 
 class SCAEncoderLayer(nn.Module):
@@ -376,14 +383,14 @@ class SCAEncoderLayer(nn.Module):
         self.cross_attn = SpatialCrossAttention_DFA3D(
             embed_dims, num_cams, dropout,
             MSDeformableAttention3D_DFA3D(embed_dims, num_heads, num_levels, num_points))
-        self.norm1 = nn.LayerNorm(embed_dims)
-        self.ffn = nn.Sequential(nn.Linear(embed_dims, ffn_dims), nn.ReLU(inplace=True), nn.Dropout(dropout),
-                                 nn.Linear(ffn_dims, embed_dims), nn.Dropout(dropout))
-        self.norm2 = nn.LayerNorm(embed_dims)
+        self.norm1 = AddLayerNorm(embed_dims)
+        self.ffn = nn.Sequential(Linear(embed_dims, ffn_dims), nn.ReLU(inplace=True), nn.Dropout(dropout),
+                                 Linear(ffn_dims, embed_dims), nn.Dropout(dropout))
+        self.norm2 = AddLayerNorm(embed_dims)
 
     def forward(self, query, **kw):
-        query = self.norm1(self.cross_attn(query, **kw))
-        return self.norm2(query + self.ffn(query))
+        query = self.norm1(*self.cross_attn(query, return_residual=True, **kw))     # norm(branch + residual)
+        return self.norm2(self.ffn(query), query)
 
 
 class CustomMSDeformableAttention(nn.Module):
@@ -401,10 +408,10 @@ class CustomMSDeformableAttention(nn.Module):
         self.num_levels, self.num_points = num_levels, num_points
         self.im2col_step, self.batch_first = im2col_step, batch_first
         self.dropout = nn.Dropout(dropout)
-        self.sampling_offsets = nn.Linear(embed_dims, num_heads * num_levels * num_points * 2)
-        self.attention_weights = nn.Linear(embed_dims, num_heads * num_levels * num_points)
-        self.value_proj = nn.Linear(embed_dims, embed_dims)
-        self.output_proj = nn.Linear(embed_dims, embed_dims)
+        self.sampling_offsets = Linear(embed_dims, num_heads * num_levels * num_points * 2)
+        self.attention_weights = Linear(embed_dims, num_heads * num_levels * num_points)
+        self.value_proj = Linear(embed_dims, embed_dims)
+        self.output_proj = Linear(embed_dims, embed_dims)
         self.init_weights()
 
     def init_weights(self):
@@ -472,15 +479,15 @@ class BEVFormerEncoderLayer(nn.Module):
         self.bev_h, self.bev_w = bev_h, bev_w
         self.self_attn = TemporalSelfAttention(embed_dims, num_heads, num_levels=1, num_points=4,
                                                dropout=dropout)
-        self.norm0 = nn.LayerNorm(embed_dims)
+        self.norm0 = AddLayerNorm(embed_dims)
         self.cross_attn = SpatialCrossAttention_DFA3D(
             embed_dims, num_cams, dropout,
             MSDeformableAttention3D_DFA3D(embed_dims, num_heads, num_levels, num_points), bev_h=bev_h,
             bev_w=bev_w, num_head=num_heads)
-        self.norm1 = nn.LayerNorm(embed_dims)
-        self.ffn = nn.Sequential(nn.Linear(embed_dims, ffn_dims), nn.ReLU(inplace=True), nn.Dropout(dropout),
-                                 nn.Linear(ffn_dims, embed_dims), nn.Dropout(dropout))
-        self.norm2 = nn.LayerNorm(embed_dims)
+        self.norm1 = AddLayerNorm(embed_dims)
+        self.ffn = nn.Sequential(Linear(embed_dims, ffn_dims), nn.ReLU(inplace=True), nn.Dropout(dropout),
+                                 Linear(ffn_dims, embed_dims), nn.Dropout(dropout))
+        self.norm2 = AddLayerNorm(embed_dims)
 
     def forward(self, query, prev_bev=None, bev_pos=None, ref_2d=None, **cross_kw):
         """query (bs, bev_h*bev_w, E); prev_bev: None or (bs*2, Q, E) = [previous, current] BEV per batch
@@ -492,10 +499,10 @@ class BEVFormerEncoderLayer(nn.Module):
                                           dtype=query.dtype)
         shapes = torch.tensor([[self.bev_h, self.bev_w]], dtype=torch.int64, device=dev)
         lsi = torch.zeros(1, dtype=torch.int64, device=dev)
-        query = self.norm0(self.self_attn(query, value=prev_bev, query_pos=bev_pos, reference_points=ref_2d,
-                                          spatial_shapes=shapes, level_start_index=lsi))
-        query = self.norm1(self.cross_attn(query, **cross_kw))
-        return self.norm2(query + self.ffn(query))
+        query = self.norm0(*self.self_attn(query, value=prev_bev, query_pos=bev_pos, reference_points=ref_2d,
+                                           spatial_shapes=shapes, level_start_index=lsi, return_residual=True))
+        query = self.norm1(*self.cross_attn(query, return_residual=True, **cross_kw))
+        return self.norm2(self.ffn(query), query)
 
 
 class SCAEncoderStack(nn.Module):

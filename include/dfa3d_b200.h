@@ -295,6 +295,32 @@ int dfa3d_fused_backward_f64(const dfa3d_problem *p, const double *value, const 
                              const double *attn, const double *grad_out, double *grad_value,
                              double *grad_dist, double *grad_loc3, double *grad_attn, void *stream);
 
+/* ---- row operations of the encoder layer around the operator ------------------------------------
+ * The layer applies norm(x + branch(x)) after each block (BEVFormer_DFA3D/projects/mmdet3d_plugin/
+ * bevformer/modules/encoder.py:363-411: self_attn, norm, cross_attn, norm, ffn, norm; the reference
+ * builds the norms as torch LayerNorm and adds the residual inside each attention / FFN module).
+ * fp32, rows of E columns, E a multiple of 4 up to 1024 (multiples of 128 use every lane), all row
+ * pointers 16-byte aligned.
+ *
+ * y = LayerNorm(x + residual) * gamma + beta over the last dimension (biased variance, eps inside the
+ * square root, like torch.nn.LayerNorm).  residual and sum_out may be NULL together (plain LayerNorm of
+ * x); with a residual, sum_out receives x + residual, the tensor the backward reads.  mean and rstd
+ * (rows) receive the row statistics. */
+int dfa3d_add_layer_norm_forward(const float *x, const float *residual, const float *gamma,
+                                 const float *beta, int64_t rows, int32_t E, float eps, float *sum_out,
+                                 float *y, float *mean, float *rstd, void *stream);
+
+/* Its backward.  `in` is what was normalised (x, or sum_out).  grad_in (rows, E) is overwritten (it is
+ * the gradient of x and of the residual alike); grad_gamma and grad_beta (E) are accumulated into and
+ * must be zeroed by the caller. */
+int dfa3d_layer_norm_backward(const float *grad_y, const float *in, const float *gamma,
+                              const float *mean, const float *rstd, int64_t rows, int32_t E,
+                              float *grad_in, float *grad_gamma, float *grad_beta, void *stream);
+
+/* dst[c] += sum over rows of src[r, c]: the bias gradient of a Linear layer (torch computes it as
+ * grad_output.sum(0)).  cols a multiple of 4; dst accumulated into, zeroed by the caller. */
+int dfa3d_column_sum(const float *src, int64_t rows, int32_t cols, float *dst, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -114,6 +114,21 @@ def test_validation_returns_codes_not_crashes(lib_built):
     half = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, _lib.DTYPE_F16, _lib.DTYPE_F16, 2)
     assert lib.dfa3d_fused_forward(ctypes.byref(half), *([None] * 9)) == -1 and b"null" in lib.dfa3d_last_error()
     assert lib.dfa3d_dist_from_logits_backward(None, 1, 64, 0, 4, None, 2, None, 1, 16, 0, None, None, None) == -1
+    # encoder-layer row operations: sizes first, then pointers
+    ln_f, ln_b, cs = lib.dfa3d_add_layer_norm_forward, lib.dfa3d_layer_norm_backward, lib.dfa3d_column_sum
+    assert ln_f(None, None, None, None, 0, 256, 1e-5, None, None, None, None, None) == 0
+    assert ln_f(None, None, None, None, 4, 102, 1e-5, None, None, None, None, None) == -2 and b"multiple of 4" in lib.dfa3d_last_error()
+    assert ln_f(None, None, None, None, 4, 2048, 1e-5, None, None, None, None, None) == -2
+    assert ln_f(None, None, None, None, -1, 256, 1e-5, None, None, None, None, None) == -1
+    assert ln_f(16, 16, 16, 16, 4, 256, 1e-5, None, 16, 16, 16, None) == -1 and b"together" in lib.dfa3d_last_error()
+    assert ln_f(None, None, None, None, 4, 256, 1e-5, None, None, None, None, None) == -1 and b"null" in lib.dfa3d_last_error()
+    assert ln_f(8, None, 16, 16, 4, 256, 1e-5, None, 16, 16, 16, None) == -1 and b"aligned" in lib.dfa3d_last_error()
+    assert ln_b(None, None, None, None, None, 0, 256, None, None, None, None) == 0
+    assert ln_b(None, None, None, None, None, 4, 256, None, None, None, None) == -1
+    assert ln_b(None, None, None, None, None, 4, 130, None, None, None, None) == -2
+    assert cs(None, 0, 8, None, None) == 0 and cs(None, 4, 0, None, None) == 0
+    assert cs(None, 4, 6, None, None) == -2 and b"multiple of 4" in lib.dfa3d_last_error()
+    assert cs(None, 4, 8, None, None) == -1 and cs(None, -1, 8, None, None) == -1
     # a dist map needs both of its sizes
     bad = _lib.Problem(1, 4, 1, 4, 2, 1, 1, 1, 0, 0, 2, 3, 0)
     assert lib.dfa3d_fused_forward(ctypes.byref(bad), *([None] * 9)) == -1 and b"dist_map" in lib.dfa3d_last_error()

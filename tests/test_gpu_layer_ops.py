@@ -1,0 +1,96 @@
+"""Encoder-layer row operations (residual add + LayerNorm, bias-gradient column sums) against torch's own
+LayerNorm / Linear in float32 and float64."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("with_residual", [False, True], ids=["plain", "residual"])
+@pytest.mark.parametrize("rows,E", [(1, 128), (3, 4), (50, 32), (77, 200), (37, 256), (1000, 256), (5003, 384), (129, 640), (64, 1024)])
+def test_add_layer_norm_matches_torch(lib_built, rows, E, with_residual):
+    from dfa3d_b200.layer_ops import AddLayerNorm
+    g = torch.Generator().manual_seed(rows + E)
+    x = (torch.randn(rows, E, generator=g) * 2 + 0.5).to(DEV)
+    r = torch.randn(rows, E, generator=g).to(DEV) if with_residual else None
+    go = torch.randn(rows, E, generator=g).to(DEV)
+    ln = AddLayerNorm(E).to(DEV)
+    with torch.no_grad():
+        ln.weight.copy_(torch.randn(E, generator=g)); ln.bias.copy_(torch.randn(E, generator=g))
+
+    def run(fn, dtype):
+        leaves = [t.detach().to(dtype).requires_grad_(True) if t is not None else None
+                  for t in (x, r, ln.weight, ln.bias)]
+        y = fn(*leaves)
+        y.backward(go.to(dtype))
+        return [y] + [t.grad for t in leaves if t is not None]
+
+    def mine(a, b, w, bias):
+        from dfa3d_b200.layer_ops import AddLayerNormFunction
+        return AddLayerNormFunction.apply(a, b, w, bias, ln.eps)
+
+    def torch_ln(a, b, w, bias):
+        return F.layer_norm(a if b is None else a + b, (E,), w, bias, ln.eps)
+
+    got, want = run(mine, torch.float32), run(torch_ln, torch.float64)
+    names = ["y", "grad_x"] + (["grad_residual"] if with_residual else []) + ["grad_weight", "grad_bias"]
+    for n, a, b in zip(names, got, want):
+        # sums over rows (weight / bias gradients) carry the rounding of `rows` float32 additions
+        tol = dict(rtol=2e-4, atol_frac=2e-6) if n.startswith("grad_w") or n.startswith("grad_b") \
+            else dict(rtol=1e-4, atol_frac=1e-5) if n.startswith("grad") else dict(rtol=1e-5, atol_frac=2e-6)
+        assert_close(n, a, b.float(), **tol)
+    # the module form, 3-D input
+    y3 = ln(x.view(1, rows, E), None if r is None else r.view(1, rows, E))
+    assert y3.shape == (1, rows, E) and torch.equal(y3.view(rows, E), got[0])
+
+
+def test_add_layer_norm_state_dict_is_layer_norm(lib_built):
+    from dfa3d_b200.layer_ops import AddLayerNorm
+    a, b = AddLayerNorm(256), torch.nn.LayerNorm(256)
+    assert list(a.state_dict()) == list(b.state_dict())
+    b.load_state_dict(a.state_dict())
+
+
+def test_layer_op_argument_checks(lib_built):
+    from dfa3d_b200.layer_ops import AddLayerNorm, column_sum
+    with pytest.raises(RuntimeError, match="multiple of 4"):
+        AddLayerNorm(102).to(DEV)(torch.zeros(4, 102, device=DEV))
+    with pytest.raises(RuntimeError, match="float32 CUDA"):
+        AddLayerNorm(128)(torch.zeros(4, 128))
+    with pytest.raises(RuntimeError, match="does not match"):
+        AddLayerNorm(128).to(DEV)(torch.zeros(4, 128, device=DEV), torch.zeros(3, 128, device=DEV))
+    with pytest.raises(RuntimeError, match="multiple of 4"):
+        column_sum(torch.zeros(4, 6, device=DEV))
+    assert column_sum(torch.zeros(0, 8, device=DEV)).tolist() == [0.0] * 8
+    empty = AddLayerNorm(128).to(DEV)(torch.zeros(0, 128, device=DEV))
+    assert empty.shape == (0, 128)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 4), (7, 12), (1000, 256), (40001, 512), (333, 772), (184950, 256)])
+def test_column_sum_matches_torch(lib_built, rows, cols):
+    from dfa3d_b200.layer_ops import column_sum
+    g = torch.Generator().manual_seed(rows)
+    src = torch.randn(rows, cols, generator=g).to(DEV)
+    want = src.double().sum(0)
+    assert_close("column_sum", column_sum(src), want.float(), rtol=1e-5, atol=float(rows) ** 0.5 * 1e-6)
+
+
+def test_linear_matches_torch_linear(lib_built):
+    from dfa3d_b200.layer_ops import Linear
+    torch.manual_seed(3)
+    mine, ref = Linear(256, 512).to(DEV), torch.nn.Linear(256, 512).to(DEV)
+    ref.load_state_dict(mine.state_dict())
+    x = torch.randn(2, 777, 256, device=DEV)
+    go = torch.randn(2, 777, 512, device=DEV)
+    outs = []
+    for m in (mine, ref):
+        xi = x.clone().requires_grad_(True)
+        y = m(xi)
+        y.backward(go)
+        outs.append((y, xi.grad, m.weight.grad, m.bias.grad))
+    for n, a, b in zip(("y", "grad_x", "grad_weight", "grad_bias"), *outs):
+        assert_close(n, a, b, rtol=1e-4, atol_frac=1e-5)

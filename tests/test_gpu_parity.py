@@ -188,6 +188,71 @@ def test_fp16_needs_value_and_dist_in_half_together(M):
         ext.dfa3d_fused_forward(t["value"], t["dist"].half(), t["shapes"], t["lsi"], t["loc"], t["attn"], 64)
 
 
+def test_fp16_storage_in_every_entry_point(M):
+    """Each kernel instantiation that reads half storage -- caller-fused, ragged, single dist map, plain 2-D
+    attention -- against the same call with float32 storage of the same (half-rounded) numbers: the arithmetic
+    is float32 either way, so the results agree to the float32 tolerances."""
+    from dfa3d_b200 import ext
+    w = wl.WORKLOADS["odd"].with_(value_dtype="fp16", seed=52, C=32)
+    d = wl.make_inputs(w)                                      # dist (B,N,D), shared by the heads
+    t = {k: v.to(DEV) for k, v in d.items()}
+    g = torch.Generator().manual_seed(52)
+    Z = 5                                                      # anchors per pillar; divides P
+    ref_pts = (torch.rand(w.B, w.Q, Z, 3, generator=g) * 1.2 - 0.1).to(DEV)
+    off_uv = (torch.randn(w.B, w.Q, w.H, w.L, w.P, 2, generator=g) * 1.5).to(DEV)
+    off_d = torch.randn(w.B, w.Q, w.H, w.L, w.P, generator=g).to(DEV)
+    logits = torch.randn(w.B, w.Q, w.H, w.L * w.P, generator=g).to(DEV)
+    # per-camera row offsets for the ragged calls: camera b keeps its first Q - b queries
+    keep = [w.Q - b for b in range(w.B)]
+    qoff = torch.tensor([0] + list(np.cumsum(keep)), dtype=torch.int32, device=DEV)
+    rows = lambda x: torch.cat([x[b, :keep[b]] for b in range(w.B)]).contiguous()
+    mh, mw = w.levels[1]
+    dmap = torch.randn(w.B, mh * mw, w.D, generator=g).softmax(-1).half().float().to(DEV)
+
+    def both(fn):
+        """fn(value, dist) -> list of tensors, once with float32 and once with half storage."""
+        a = fn(t["value"], t["dist"], dmap)
+        b = fn(t["value"].half(), t["dist"].half(), dmap.half())
+        assert len(a) == len(b)
+        return zip(a, b)
+
+    def fused(v, p, m):
+        out, ds = ext.dfa3d_fused_forward(v, p, t["shapes"], t["lsi"], t["loc"], t["attn"], 64)
+        outm, _ = ext.dfa3d_fused_forward(v, m, t["shapes"], t["lsi"], t["loc"], t["attn"], 64, dist_map=(mh, mw))
+        gv = torch.zeros_like(t["value"]); gm = torch.zeros_like(dmap)
+        gl = torch.empty_like(t["loc"]); ga = torch.empty_like(t["attn"])
+        ext.dfa3d_fused_backward(v, m, t["shapes"], t["lsi"], t["loc"], t["attn"], t["grad_out"], gv, gm, gl, ga, 64,
+                                 dist_map=(mh, mw))
+        return [out, ds, outm, gv, gm, ga]
+
+    def ragged(v, p, m):
+        loc, attn, go = rows(t["loc"]), rows(t["attn"]), rows(t["grad_out"])
+        out, ds = ext.dfa3d_fused_forward_ragged(v, p, t["shapes"], t["lsi"], loc, attn, qoff, w.Q)
+        gv = torch.zeros_like(t["value"]); gd = torch.zeros_like(t["dist"])
+        gl = torch.empty_like(loc); ga = torch.empty_like(attn)
+        ext.dfa3d_fused_backward_ragged(v, p, t["shapes"], t["lsi"], loc, attn, qoff, w.Q, go, gv, gd, gl, ga)
+        return [out, ds, gv, gd, ga]
+
+    def caller_fused(v, p, m):
+        out = ext.dfa3d_attn3d_forward(v, p, t["shapes"], t["lsi"], ref_pts, off_uv, off_d, logits)
+        gv = torch.zeros_like(t["value"]); gd = torch.zeros_like(t["dist"])
+        guv = torch.empty_like(off_uv); gdd = torch.empty_like(off_d); glg = torch.empty_like(logits)
+        ext.dfa3d_attn3d_backward(v, p, t["shapes"], t["lsi"], ref_pts, off_uv, off_d, logits, t["grad_out"], gv, gd,
+                                  guv, gdd, glg)
+        return [out, gv, gd, guv, gdd, glg]
+
+    def plain_2d(v, p, m):
+        s2, l2 = t["shapes"][:, :2].contiguous(), t["loc"][..., :2].contiguous()
+        out = ext.ms_deform_attn_forward(v, s2, t["lsi"], l2, t["attn"], 64)
+        gv = torch.zeros_like(t["value"]); gl = torch.empty_like(l2); ga = torch.empty_like(t["attn"])
+        ext.ms_deform_attn_backward(v, s2, t["lsi"], l2, t["attn"], t["grad_out"], gv, gl, ga, 64)
+        return [out, gv, gl, ga]
+
+    for fn in (fused, ragged, caller_fused, plain_2d):
+        for i, (a, b) in enumerate(both(fn)):
+            assert_close(f"{fn.__name__}[{i}]", b, a, **BWD)
+
+
 def test_two_stage_api_matches_oracle(M):
     """MultiScaleDepthScoreSampleFunction -> WeightedMultiScaleDeformableAttnFunction with the
     gradient flowing through depth_score (unittest_DFA3D.py:11-22 drives the forward of this path)."""
