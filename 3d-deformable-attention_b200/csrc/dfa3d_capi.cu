@@ -509,6 +509,7 @@ int dfa3d_layer_norm_backward(const float *grad_y, const float *in, const float 
   REQUIRE_PTR(grad_y); REQUIRE_PTR(in); REQUIRE_PTR(gamma); REQUIRE_PTR(mean); REQUIRE_PTR(rstd);
   REQUIRE_PTR(grad_in); REQUIRE_PTR(grad_gamma); REQUIRE_PTR(grad_beta);
   REQUIRE_ALIGNED(grad_y); REQUIRE_ALIGNED(in); REQUIRE_ALIGNED(gamma); REQUIRE_ALIGNED(grad_in);
+  REQUIRE_ALIGNED(grad_gamma); REQUIRE_ALIGNED(grad_beta);
   return finish(dfa3d::launch_layer_norm_backward(grad_y, in, gamma, mean, rstd, rows, E, grad_in, grad_gamma,
                                                   grad_beta, (cudaStream_t)stream),
                 "dfa3d_layer_norm_backward launch");
@@ -520,7 +521,7 @@ int dfa3d_column_sum(const float *src, int64_t rows, int32_t cols, float *dst, v
   if (cols % 4 != 0) return fail(DFA3D_ERR_UNSUPPORTED, "cols=%d must be a multiple of 4", cols);
   if (rows == 0 || cols == 0) return DFA3D_OK;
   REQUIRE_PTR(src); REQUIRE_PTR(dst);
-  REQUIRE_ALIGNED(src);
+  REQUIRE_ALIGNED(src); REQUIRE_ALIGNED(dst);
   return finish(dfa3d::launch_column_sum(src, rows, cols, dst, (cudaStream_t)stream), "dfa3d_column_sum launch");
 }
 

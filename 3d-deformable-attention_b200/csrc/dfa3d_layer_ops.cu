@@ -33,8 +33,11 @@ __device__ __forceinline__ float4 ld4(const float *p) { return __ldg(reinterpret
 __device__ __forceinline__ float4 ld4_stream(const float *p) { return __ldcs(reinterpret_cast<const float4 *>(p)); }
 __device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
 
-__device__ __forceinline__ void red_add(float *addr, float a) {
-  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
+// One 16-byte vector reduction into global memory (sm_90+).
+__device__ __forceinline__ void red_add_v4(float *addr, float4 v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
 }
 
 // Rows of E columns, E a multiple of 4 with 128 * (K - 1) < E <= 128 * K; lane l holds the float4 groups
@@ -104,7 +107,6 @@ layer_norm_backward_kernel(const float *__restrict__ grad_y, const float *__rest
                            const float *__restrict__ rstd_in, long long rows, int E,
                            float *__restrict__ grad_in, float *__restrict__ grad_gamma,
                            float *__restrict__ grad_beta) {
-  constexpr int EK = 128 * K;
   const float inv_e = 1.f / (float)E;
   __shared__ float4 part[kLnWarps][32 * K];      // one warp's per-column partial sums
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -156,20 +158,24 @@ layer_norm_backward_kernel(const float *__restrict__ grad_y, const float *__rest
     for (int j = 0; j < K; ++j) part[warp][lane + 32 * j] = pass == 0 ? dg[j] : db[j];
     __syncthreads();
     float *dst = pass == 0 ? grad_gamma : grad_beta;
-    const float *flat = reinterpret_cast<const float *>(&part[0][0]);
-    for (int c = threadIdx.x; c < E; c += kLnThreads) {
-      float t = 0.f;
+    for (int c4 = threadIdx.x; c4 * 4 < E; c4 += kLnThreads) {
+      float4 t = part[0][c4];
 #pragma unroll
-      for (int w = 0; w < kLnWarps; ++w) t += flat[w * EK + c];
-      red_add(dst + c, t);
+      for (int w = 1; w < kLnWarps; ++w) {
+        const float4 u = part[w][c4];
+        t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+      }
+      red_add_v4(dst + c4 * 4, t);
     }
     __syncthreads();
   }
 }
 
-// Column sums: a CTA is 64 float4 column groups x 4 row lanes; blockIdx.y picks the band of 256 columns,
-// blockIdx.x the rows (grid-strided).  dst is accumulated into (caller-zeroed).
-constexpr int kCsGroups = 64, kCsLanes = 4, kCsThreads = kCsGroups * kCsLanes;
+// Column sums: a CTA is 64 float4 column groups x 8 row lanes; blockIdx.y picks the band of 256 columns,
+// blockIdx.x the rows (grid-strided).  dst is accumulated into (caller-zeroed).  Few, long-lived CTAs: every
+// CTA ends with one vector reduction per column group into the same few sectors of dst, and those
+// serialise in L2.
+constexpr int kCsGroups = 64, kCsLanes = 8, kCsThreads = kCsGroups * kCsLanes;
 
 __global__ void __launch_bounds__(kCsThreads)
 column_sum_kernel(const float *__restrict__ src, long long rows, int cols, float *__restrict__ dst) {
@@ -201,7 +207,7 @@ column_sum_kernel(const float *__restrict__ src, long long rows, int cols, float
     for (int i = 1; i < kCsLanes; ++i) {
       t.x += part[i][grp].x; t.y += part[i][grp].y; t.z += part[i][grp].z; t.w += part[i][grp].w;
     }
-    red_add(dst + col, t.x); red_add(dst + col + 1, t.y); red_add(dst + col + 2, t.z); red_add(dst + col + 3, t.w);
+    red_add_v4(dst + col, t);
   }
 }
 
@@ -261,7 +267,7 @@ cudaError_t launch_layer_norm_backward(const float *grad_y, const float *in, con
 cudaError_t launch_column_sum(const float *src, long long rows, int cols, float *dst, cudaStream_t s) {
   if (rows == 0 || cols == 0) return cudaSuccess;
   const unsigned bands = (unsigned)((cols / 4 + kCsGroups - 1) / kCsGroups);
-  long long gx = (long long)kSms * 8 / bands;
+  long long gx = (long long)kSms * 2 / bands;                            // two 512-thread CTAs per SM
   const long long most = (rows + kCsLanes * 8 - 1) / (kCsLanes * 8);     // at least 8 rows per thread
   if (gx > most) gx = most;
   if (gx < 1) gx = 1;

@@ -80,8 +80,8 @@ class AddLayerNormFunction(Function):
         E = inp.shape[-1]
         grad_y = grad_y.contiguous()
         grad_in = torch.empty_like(inp)
-        grad_w = torch.zeros(E, dtype=torch.float32, device=inp.device)
-        grad_b = torch.zeros(E, dtype=torch.float32, device=inp.device)
+        grad_wb = torch.zeros((2, E), dtype=torch.float32, device=inp.device)     # one fill for both
+        grad_w, grad_b = grad_wb[0], grad_wb[1]
         with torch.cuda.device(inp.device):
             _lib.call_plain("dfa3d_layer_norm_backward", grad_y.data_ptr(), inp.data_ptr(), weight.data_ptr(),
                             mean.data_ptr(), rstd.data_ptr(), mean.numel(), E, grad_in.data_ptr(),

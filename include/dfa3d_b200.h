@@ -312,13 +312,14 @@ int dfa3d_add_layer_norm_forward(const float *x, const float *residual, const fl
 
 /* Its backward.  `in` is what was normalised (x, or sum_out).  grad_in (rows, E) is overwritten (it is
  * the gradient of x and of the residual alike); grad_gamma and grad_beta (E) are accumulated into and
- * must be zeroed by the caller. */
+ * must be zeroed by the caller; both 16-byte aligned. */
 int dfa3d_layer_norm_backward(const float *grad_y, const float *in, const float *gamma,
                               const float *mean, const float *rstd, int64_t rows, int32_t E,
                               float *grad_in, float *grad_gamma, float *grad_beta, void *stream);
 
 /* dst[c] += sum over rows of src[r, c]: the bias gradient of a Linear layer (torch computes it as
- * grad_output.sum(0)).  cols a multiple of 4; dst accumulated into, zeroed by the caller. */
+ * grad_output.sum(0)).  cols a multiple of 4; dst accumulated into, zeroed by the caller, 16-byte
+ * aligned like src. */
 int dfa3d_column_sum(const float *src, int64_t rows, int32_t cols, float *dst, void *stream);
 
 #ifdef __cplusplus
