@@ -9,7 +9,7 @@ and torch's Linear.  Here
     whose forward takes an optional residual: one kernel forms the sum and normalises it, one kernel
     produces the input gradient and the weight / bias gradients.
   * ``Linear`` is ``torch.nn.Linear`` whose bias gradient is a single column-sum kernel; the matrix
-    products stay with cuBLAS.
+    products stay with cuBLAS (the weight gradient as a batch of row slices, see ``weight_gradient``).
 
 float32 CUDA tensors only; like the rest of the package there is no fallback path.
 """
@@ -102,6 +102,25 @@ class AddLayerNorm(nn.LayerNorm):
         return AddLayerNormFunction.apply(x, residual, self.weight, self.bias, self.eps)
 
 
+_SPLIT_ROWS, _SPLITS = 16384, 16
+
+
+def weight_gradient(grad_out2, x2):
+    """grad_out2 (rows, out)ᵀ @ x2 (rows, in) -> (out, in).  With many rows and a small result the product is
+    one long reduction that cuBLAS runs on few CTAs (measured 60-206 us for 40 000-185 000 rows of 256-768
+    columns, 4-7 times the time of reading the operands); as a batch of 16 row slices plus a sum of the 16
+    partial results it takes 25-80 us."""
+    rows = grad_out2.shape[0]
+    if rows < _SPLIT_ROWS:
+        return grad_out2.t() @ x2
+    k = rows // _SPLITS
+    head = k * _SPLITS
+    w = torch.bmm(grad_out2[:head].view(_SPLITS, k, -1).transpose(1, 2), x2[:head].view(_SPLITS, k, -1)).sum(0)
+    if head < rows:
+        w.addmm_(grad_out2[head:].t(), x2[head:])
+    return w
+
+
 class LinearFunction(Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -121,7 +140,7 @@ class LinearFunction(Function):
         if ctx.needs_input_grad[0]:
             grad_x = (g2 @ weight).view(x.shape)
         if ctx.needs_input_grad[1]:
-            grad_w = g2.t() @ x.reshape(-1, x.shape[-1])
+            grad_w = weight_gradient(g2, x.reshape(-1, x.shape[-1]))
         if ctx.needs_input_grad[2]:
             grad_b = column_sum(g2)
         return grad_x, grad_w, grad_b

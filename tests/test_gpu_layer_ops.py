@@ -79,13 +79,14 @@ def test_column_sum_matches_torch(lib_built, rows, cols):
     assert_close("column_sum", column_sum(src), want.float(), rtol=1e-5, atol=float(rows) ** 0.5 * 1e-6)
 
 
-def test_linear_matches_torch_linear(lib_built):
+@pytest.mark.parametrize("rows", [777, 16384 + 5])      # below and above the row count that splits the weight gradient
+def test_linear_matches_torch_linear(lib_built, rows):
     from dfa3d_b200.layer_ops import Linear
     torch.manual_seed(3)
     mine, ref = Linear(256, 512).to(DEV), torch.nn.Linear(256, 512).to(DEV)
     ref.load_state_dict(mine.state_dict())
-    x = torch.randn(2, 777, 256, device=DEV)
-    go = torch.randn(2, 777, 512, device=DEV)
+    x = torch.randn(2, rows, 256, device=DEV)
+    go = torch.randn(2, rows, 512, device=DEV)
     outs = []
     for m in (mine, ref):
         xi = x.clone().requires_grad_(True)
