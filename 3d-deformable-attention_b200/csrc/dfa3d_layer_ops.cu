@@ -118,37 +118,61 @@ layer_norm_backward_kernel(const float *__restrict__ grad_y, const float *__rest
     dg[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     db[j] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  for (long long row = warp0; row < rows; row += stride) {
-    const float mean = __ldg(mean_in + row), rstd = __ldg(rstd_in + row);
-    float4 g[K], xh[K];
-    float s1 = 0.f, s2 = 0.f;
+  // R rows of a warp are in flight together (narrow rows leave registers for it): their loads are issued
+  // before any of them is reduced
+  constexpr int R = K <= 2 ? 2 : 1;
+  for (long long row0 = warp0; row0 < rows; row0 += stride * R) {
+    float4 g[R][K], xh[R][K];
+    float mean[R], rstd[R];
 #pragma unroll
-    for (int j = 0; j < K; ++j) {
-      const int c = (lane + 32 * j) * 4;
-      g[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-      xh[j] = g[j];
-      if (c >= E) continue;
-      g[j] = ld4_stream(grad_y + row * E + c);
-      const float4 v = ld4_stream(in + row * E + c);
-      xh[j] = make_float4((v.x - mean) * rstd, (v.y - mean) * rstd, (v.z - mean) * rstd, (v.w - mean) * rstd);
-      dg[j].x += g[j].x * xh[j].x; dg[j].y += g[j].y * xh[j].y;
-      dg[j].z += g[j].z * xh[j].z; dg[j].w += g[j].w * xh[j].w;
-      db[j].x += g[j].x; db[j].y += g[j].y; db[j].z += g[j].z; db[j].w += g[j].w;
-      const float4 gam = ld4(gamma + c);
-      g[j].x *= gam.x; g[j].y *= gam.y; g[j].z *= gam.z; g[j].w *= gam.w;
-      s1 += (g[j].x + g[j].y) + (g[j].z + g[j].w);
-      s2 += (g[j].x * xh[j].x + g[j].y * xh[j].y) + (g[j].z * xh[j].z + g[j].w * xh[j].w);
+    for (int r = 0; r < R; ++r) {
+      const long long row = row0 + r * stride;
+      const bool live = row < rows;
+      mean[r] = live ? __ldg(mean_in + row) : 0.f;
+      rstd[r] = live ? __ldg(rstd_in + row) : 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        const int c = (lane + 32 * j) * 4;
+        g[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        xh[r][j] = g[r][j];
+        if (live && c < E) {
+          g[r][j] = ld4_stream(grad_y + row * E + c);
+          xh[r][j] = ld4_stream(in + row * E + c);
+        }
+      }
     }
-    const float c1 = warp_sum(s1) * inv_e, c2 = warp_sum(s2) * inv_e;
 #pragma unroll
-    for (int j = 0; j < K; ++j) {
-      if ((lane + 32 * j) * 4 >= E) continue;
-      float4 o;
-      o.x = rstd * (g[j].x - c1 - xh[j].x * c2);
-      o.y = rstd * (g[j].y - c1 - xh[j].y * c2);
-      o.z = rstd * (g[j].z - c1 - xh[j].z * c2);
-      o.w = rstd * (g[j].w - c1 - xh[j].w * c2);
-      st4(grad_in + row * E + (lane + 32 * j) * 4, o);
+    for (int r = 0; r < R; ++r) {
+      const long long row = row0 + r * stride;
+      if (row >= rows) break;
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        const int c = (lane + 32 * j) * 4;
+        if (c >= E) continue;
+        float4 &G = g[r][j], &X = xh[r][j];
+        X = make_float4((X.x - mean[r]) * rstd[r], (X.y - mean[r]) * rstd[r], (X.z - mean[r]) * rstd[r],
+                        (X.w - mean[r]) * rstd[r]);
+        dg[j].x += G.x * X.x; dg[j].y += G.y * X.y; dg[j].z += G.z * X.z; dg[j].w += G.w * X.w;
+        db[j].x += G.x; db[j].y += G.y; db[j].z += G.z; db[j].w += G.w;
+        const float4 gam = ld4(gamma + c);
+        G.x *= gam.x; G.y *= gam.y; G.z *= gam.z; G.w *= gam.w;
+        s1 += (G.x + G.y) + (G.z + G.w);
+        s2 += (G.x * X.x + G.y * X.y) + (G.z * X.z + G.w * X.w);
+      }
+      const float c1 = warp_sum(s1) * inv_e, c2 = warp_sum(s2) * inv_e;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        const int c = (lane + 32 * j) * 4;
+        if (c >= E) continue;
+        const float4 G = g[r][j], X = xh[r][j];
+        float4 o;
+        o.x = rstd[r] * (G.x - c1 - X.x * c2);
+        o.y = rstd[r] * (G.y - c1 - X.y * c2);
+        o.z = rstd[r] * (G.z - c1 - X.z * c2);
+        o.w = rstd[r] * (G.w - c1 - X.w * c2);
+        st4(grad_in + row * E + c, o);
+      }
     }
   }
   // combine the CTA's warps, then one reduction per column and CTA; gamma first, beta second
@@ -246,16 +270,18 @@ cudaError_t launch_layer_norm_backward(const float *grad_y, const float *in, con
                                        float *grad_in, float *grad_gamma, float *grad_beta,
                                        cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
-  // fewer, longer-lived CTAs than the forward: each ends with E reductions per output
+  // as many CTAs as are resident at once (the kernel's launch bounds), each with at least 8 rows per warp:
+  // every CTA ends with E/4 vector reductions per output
+  const int K = (E + 127) / 128;
   const long long want = (rows + kLnWarps * 8 - 1) / (kLnWarps * 8);
-  const long long cap = (long long)kSms * 2;
+  const long long cap = (long long)kSms * (K <= 1 ? kCtasPerSm : (K == 2 ? 3 : (K <= 4 ? 2 : 1)));
   const unsigned grid = (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
 #define DFA3D_LN_BWD(K)                                                                               \
   case K:                                                                                             \
     layer_norm_backward_kernel<K><<<grid, kLnThreads, 0, s>>>(grad_y, in, gamma, mean, rstd, rows, E,  \
                                                               grad_in, grad_gamma, grad_beta);        \
     break;
-  switch ((E + 127) / 128) {
+  switch (K) {
     DFA3D_LN_BWD(1) DFA3D_LN_BWD(2) DFA3D_LN_BWD(3) DFA3D_LN_BWD(4)
     DFA3D_LN_BWD(5) DFA3D_LN_BWD(6) DFA3D_LN_BWD(7) DFA3D_LN_BWD(8)
     default: return cudaErrorInvalidValue;

@@ -153,3 +153,59 @@ class Linear(nn.Linear):
         if self.bias is None or self.out_features % 4 != 0:
             return super().forward(x)
         return LinearFunction.apply(x, self.weight, self.bias)
+
+
+def _time_ms(fn, launches=200):
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / launches
+
+
+def measure(device="cuda"):
+    """CUDA-event timings of the three kernels at the encoder stack's sizes, called through the C entry
+    points on preallocated tensors, with torch's kernels for the same work beside them.  Returns a list of
+    dicts (GB/s = bytes every operand and result is read / written once, over the time)."""
+    out = []
+    st = torch.cuda.current_stream(device).cuda_stream
+    for rows, cols in ((184950, 256), (60000, 768), (60000, 512), (40000, 256)):
+        src = torch.randn(rows, cols, device=device)
+        dst = torch.zeros(cols, device=device)
+        ms = _time_ms(lambda: _lib.call_plain("dfa3d_column_sum", src.data_ptr(), rows, cols, dst.data_ptr(), st))
+        out.append({"kernel": "column_sum", "rows": rows, "cols": cols, "ms": ms,
+                    "GB/s": rows * cols * 4 / ms / 1e6, "torch_ms": _time_ms(lambda: src.sum(0))})
+    for rows, E in ((240000, 256), (40000, 256)):
+        x, r, go = (torch.randn(rows, E, device=device) for _ in range(3))
+        w, b = torch.ones(E, device=device), torch.zeros(E, device=device)
+        s, y, gi = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+        mean, rstd = torch.empty(rows, device=device), torch.empty(rows, device=device)
+        gwb = torch.zeros(2, E, device=device)
+        fwd = lambda: _lib.call_plain("dfa3d_add_layer_norm_forward", x.data_ptr(), r.data_ptr(), w.data_ptr(),
+                                      b.data_ptr(), rows, E, 1e-5, s.data_ptr(), y.data_ptr(), mean.data_ptr(),
+                                      rstd.data_ptr(), st)
+        bwd = lambda: _lib.call_plain("dfa3d_layer_norm_backward", go.data_ptr(), s.data_ptr(), w.data_ptr(),
+                                      mean.data_ptr(), rstd.data_ptr(), rows, E, gi.data_ptr(), gwb[0].data_ptr(),
+                                      gwb[1].data_ptr(), st)
+        f_ms, b_ms = _time_ms(fwd), _time_ms(bwd)
+        xs = (x + r).requires_grad_(True)
+        ln = torch.nn.LayerNorm(E).to(device)
+        t_f = _time_ms(lambda: torch.nn.functional.layer_norm(x + r, (E,), ln.weight, ln.bias))
+        yy = ln(xs)
+        t_b = _time_ms(lambda: torch.autograd.grad(yy, (xs, ln.weight, ln.bias), go, retain_graph=True))
+        out.append({"kernel": "add_layer_norm_forward", "rows": rows, "cols": E, "ms": f_ms,
+                    "GB/s": 4 * rows * E * 4 / f_ms / 1e6, "torch_ms": t_f})
+        out.append({"kernel": "layer_norm_backward", "rows": rows, "cols": E, "ms": b_ms,
+                    "GB/s": 3 * rows * E * 4 / b_ms / 1e6, "torch_ms": t_b})
+    return out
+
+
+if __name__ == "__main__":      # python -m dfa3d_b200.layer_ops   (with the package directory on PYTHONPATH)
+    import json
+    for line in measure():
+        print(json.dumps(line))

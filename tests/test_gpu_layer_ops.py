@@ -95,3 +95,10 @@ def test_linear_matches_torch_linear(lib_built, rows):
         outs.append((y, xi.grad, m.weight.grad, m.bias.grad))
     for n, a, b in zip(("y", "grad_x", "grad_weight", "grad_bias"), *outs):
         assert_close(n, a, b, rtol=1e-4, atol_frac=1e-5)
+
+
+def test_measure_times_every_row_kernel(lib_built):
+    from dfa3d_b200 import layer_ops
+    got = layer_ops.measure(DEV)
+    assert {g["kernel"] for g in got} == {"column_sum", "add_layer_norm_forward", "layer_norm_backward"}
+    assert all(g["ms"] > 0 and g["GB/s"] > 0 and g["torch_ms"] > 0 for g in got)
