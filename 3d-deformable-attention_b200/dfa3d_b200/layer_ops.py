@@ -11,7 +11,8 @@ and torch's Linear.  Here
   * ``Linear`` is ``torch.nn.Linear`` whose bias gradient is a single column-sum kernel; the matrix
     products stay with cuBLAS (the weight gradient as a batch of row slices, see ``weight_gradient``).
 
-float32 CUDA tensors only; like the rest of the package there is no fallback path.
+float32 CUDA tensors only (under autocast the inputs are cast to float32, like the package's ``*_fp32``
+Functions); like the rest of the package there is no fallback path.
 """
 import torch
 import torch.nn as nn
@@ -44,6 +45,7 @@ def column_sum(src):
 
 class AddLayerNormFunction(Function):
     @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float32)
     def forward(ctx, x, residual, weight, bias, eps):
         """LayerNorm(x + residual) over the last dimension; residual may be None."""
         for t, n in ((x, "x"), (weight, "weight"), (bias, "bias")):
@@ -74,6 +76,7 @@ class AddLayerNormFunction(Function):
         return y
 
     @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
     @once_differentiable
     def backward(ctx, grad_y):
         inp, weight, mean, rstd = ctx.saved_tensors
@@ -123,6 +126,7 @@ def weight_gradient(grad_out2, x2):
 
 class LinearFunction(Function):
     @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float32)
     def forward(ctx, x, weight, bias):
         ctx.save_for_backward(x, weight)
         # written into a tensor of its own (F.linear returns a view of the 2-D product for inputs of more
@@ -132,6 +136,7 @@ class LinearFunction(Function):
         return y
 
     @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
     @once_differentiable
     def backward(ctx, grad_out):
         x, weight = ctx.saved_tensors

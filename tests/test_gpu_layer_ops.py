@@ -102,3 +102,17 @@ def test_measure_times_every_row_kernel(lib_built):
     got = layer_ops.measure(DEV)
     assert {g["kernel"] for g in got} == {"column_sum", "add_layer_norm_forward", "layer_norm_backward"}
     assert all(g["ms"] > 0 and g["GB/s"] > 0 and g["torch_ms"] > 0 for g in got)
+
+
+def test_layer_ops_compute_in_float32_under_autocast(lib_built):
+    from dfa3d_b200.layer_ops import AddLayerNorm, Linear
+    torch.manual_seed(0)
+    ln, lin = AddLayerNorm(128).to(DEV), Linear(128, 64).to(DEV)
+    x = torch.randn(9, 128, device=DEV, requires_grad=True)
+    want = ln(lin(x).repeat(1, 2), x)
+    with torch.autocast("cuda", dtype=torch.float16):
+        got = ln(lin(x.half()).repeat(1, 2), x.half())
+    assert got.dtype == torch.float32
+    assert_close("autocast", got, want, rtol=5e-3, atol=5e-3)
+    got.sum().backward()
+    assert x.grad is not None and torch.isfinite(x.grad).all()
