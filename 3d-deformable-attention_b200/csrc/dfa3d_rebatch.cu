@@ -152,15 +152,24 @@ rebatch_combine_kernel(const float *src, const int32_t *row_of, const int32_t *o
     float acc[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-    for (int cam = 0; cam < cams; ++cam) {
-      const int r = row_of[(long long)cam * Q + q];
-      if (r < 0) continue;
-      const float *sp = src + ((long long)j * T + r) * W;
+    // eight cameras at a time: their row indices first, then the rows, so that the loads of one thread
+    // overlap instead of forming an index -> row chain per camera
+    for (int cam0 = 0; cam0 < cams; cam0 += 8) {
+      int r[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r[i] = cam0 + i < cams ? __ldg(row_of + (long long)(cam0 + i) * Q + q) : -1;
       if (VEC == 4) {
-        const float4 x = __ldg(reinterpret_cast<const float4 *>(sp) + v);
-        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+        float4 x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          x[i] = r[i] >= 0 ? __ldg(reinterpret_cast<const float4 *>(src + ((long long)j * T + r[i]) * W) + v)
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { acc[0] += x[i].x; acc[1] += x[i].y; acc[2] += x[i].z; acc[3] += x[i].w; }
       } else {
-        acc[0] += __ldg(sp + v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (r[i] >= 0) acc[0] += __ldg(src + ((long long)j * T + r[i]) * W + v);
       }
     }
     const float s = scale ? scale[jq] : 1.f;
