@@ -417,6 +417,7 @@ static void launch_backward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
     case 4:  dfa3d_backward_kernel<VT, DT, 4 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 8:  dfa3d_backward_kernel<VT, DT, 8 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 16: dfa3d_backward_kernel<VT, DT, 16 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    case 32: dfa3d_backward_kernel<VT, DT, 32 * V, MODE, FULL><<<grid, kThreads, 0, s>>>(a); break;
     default: {
       const dim3 g1((unsigned)((a.items_per_cam + kWarpsPerCta - 1) / kWarpsPerCta), grid.y, 1);
       dfa3d_backward_generic_kernel<VT, DT, MODE><<<g1, kThreads, 0, s>>>(a);

@@ -257,6 +257,7 @@ static void launch_forward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
     case 4:  dfa3d_forward_kernel<VT, DT, 4 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 8:  dfa3d_forward_kernel<VT, DT, 8 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
     case 16: dfa3d_forward_kernel<VT, DT, 16 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
+    case 32: dfa3d_forward_kernel<VT, DT, 32 * V, MODE, WRITE_DS, FULL><<<grid, kThreads, 0, s>>>(a); break;
     default:
       dfa3d_forward_generic_kernel<VT, DT, MODE, WRITE_DS><<<item_grid(a, (int)grid.y, 1), kThreads, 0, s>>>(a);
       break;

@@ -53,9 +53,9 @@ typedef struct dfa3d_problem {
   int32_t N;  /* pixels over all levels */
   int32_t H;  /* heads */
   int32_t C;  /* channels per head, any value up to DFA3D_MAX_CHANNELS.  Vectorised kernels: fp32 value
-                 C in {8,16,32,64}; bf16 / fp16 value C in {16,32,64,128} forward and {8,16,32,64} backward.
-                 Every other width (fp32 C = 128 and bf16 C = 128 in the backward included) runs a
-                 lane-strided kernel with the same results, several times slower. */
+                 C in {8,16,32,64,128}; bf16 / fp16 value C in {16,32,64,128,256} forward and
+                 {8,16,32,64,128} backward.  Every other width runs a lane-strided kernel with the same
+                 results, several times slower. */
   int32_t D;  /* depth bins = channel count of dist */
   int32_t L;  /* levels */
   int32_t Q;  /* queries */

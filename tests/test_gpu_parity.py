@@ -82,9 +82,9 @@ def test_fused_matches_oracle(M, name, shared_dist):
 
 
 CHANNEL_CASES = {
-    # vector kernels: C/4 in {2,4,8,16}; everything else takes the any-width kernel
+    # vector kernels: C/4 in {2,4,8,16,32}; everything else takes the any-width kernel
     "C8": dict(C=8), "C16": dict(C=16), "C64": dict(C=64, H=2), "C12_generic": dict(C=12),
-    "C20_generic": dict(C=20, H=3), "C128_generic": dict(C=128, H=1),
+    "C20_generic": dict(C=20, H=3), "C128": dict(C=128, H=1), "C256_generic": dict(C=256, H=1),
     "LP45_two_chunks": dict(levels=((6, 5), (4, 4), (3, 3), (2, 3), (1, 1)), P=9),
     "LP32_exact": dict(levels=((6, 5), (4, 4), (3, 3), (2, 3)), P=8),
     "one_pixel_levels": dict(levels=((1, 1), (1, 2)), D=1),
