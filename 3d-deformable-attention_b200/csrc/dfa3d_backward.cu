@@ -308,6 +308,127 @@ dfa3d_backward_kernel(const KArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// few points per item (L*P = 4, 8 or 16): a warp takes 32 / (L*P) consecutive items at once
+// ------------------------------------------------------------------------------------------------
+// Lane j owns point j % LP of item j / LP (full, coalesced prologue and epilogue); a group of G lanes
+// walks the rows of one item -- or a share of them when the warp holds fewer items than groups -- with
+// that item's grad_out fragment.  Same row phase as backward_item otherwise.
+template <typename VT, typename DT, int C, int MODE, int LP>
+__global__ void __launch_bounds__(kThreads, DFA3D_BWD_MIN_CTAS)
+dfa3d_backward_packed_kernel(const KArgs a) {
+  constexpr int V = RowVec4<VT>::kElems;
+  constexpr int G = C / V;
+  constexpr int R = 32 / G;
+  constexpr int K = 32 / LP;
+  constexpr int GPI = R > K ? R / K : 1;
+  constexpr int IPG = K > R ? K / R : 1;
+  constexpr int U = 4;
+  constexpr int kRows = LP * 4;
+  static_assert(G >= 4 && 32 % LP == 0 && 32 % G == 0 && kRows % (GPI * U) == 0, "unsupported packing");
+  __shared__ LevelTable lv;
+  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
+  __shared__ __align__(16) float dots[kWarpsPerCta][128];
+  stage_levels(lv, a);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % G, grp = lane / G;
+  const int b = (int)blockIdx.y + a.b0;
+  const long long cam = (long long)b * a.N * a.H * C + sub * V;
+  const VT *vbase = reinterpret_cast<const VT *>(a.value) + cam;
+  float *gvbase = a.grad_value + cam;
+  RowEntry *table = rows[warp];
+  float *dot_slots = dots[warp];
+#pragma unroll 1
+  for (int it = 0; it < DFA3D_BWD_ITEMS_PER_WARP; ++it) {
+    const unsigned first = ((blockIdx.x * DFA3D_BWD_ITEMS_PER_WARP + it) * kWarpsPerCta + warp) * K;
+    if (first >= (unsigned)a.items_per_cam) return;
+    const unsigned idx = first + lane / LP;
+    const bool live = idx < (unsigned)a.items_per_cam;
+    ItemCtx c;
+    c.b = b;
+    {
+      const unsigned q = idx / (unsigned)a.H;
+      c.h = (int)(idx - q * (unsigned)a.H);
+      c.bq = (long long)b * a.Q + q;
+    }
+    c.item = (long long)b * a.items_per_cam + idx;
+    c.pt0 = c.item * LP;
+    c.loc = a.loc + c.pt0 * a.loc_stride;
+    c.attn = a.attn + c.pt0;
+    const int j = live ? lane % LP : a.LP;       // a.LP: no such point, the lane stays idle
+    PointState st;
+    {
+      float wgt[4];
+      int off[4];
+      bwd_point<DT, MODE>(a, lv, c, j, SoftmaxStats{0.f, 1.f}, st, wgt, off);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (off[k] >= 0) off[k] += c.h * C;
+      store_rows(table, lane, off, wgt);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int t = 0; t < IPG; ++t) {
+      const int i = grp / GPI + t * (R / GPI);
+      const unsigned item_i = first + i;
+      const int base = i * kRows + (grp % GPI) * U;
+      float go[V];
+      if (item_i < (unsigned)a.items_per_cam) {
+        const float *gp = a.grad_out + (((long long)b * a.items_per_cam + item_i) * C + sub * V);
+#pragma unroll
+        for (int x = 0; x < V; x += 4) {
+          const float4 q4 = __ldg(reinterpret_cast<const float4 *>(gp + x));
+          go[x] = q4.x; go[x + 1] = q4.y; go[x + 2] = q4.z; go[x + 3] = q4.w;
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < V; ++x) go[x] = 0.f;
+      }
+#pragma unroll
+      for (int r0 = 0; r0 < kRows; r0 += GPI * U) {
+        RowEntry e[U];
+        float v[U][V];
+#pragma unroll
+        for (int u = 0; u < U; ++u) e[u] = table[base + r0 + u];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (e[u].off >= 0) {
+            RowVec4<VT>::load(vbase + e[u].off, v[u]);
+          } else {
+#pragma unroll
+            for (int x = 0; x < V; ++x) v[u][x] = 0.f;
+          }
+        }
+        float d[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          d[u] = 0.f;
+#pragma unroll
+          for (int x = 0; x < V; ++x) d[u] = fmaf(v[u][x], go[x], d[u]);
+        }
+        int u_mine;
+        const float f = fold_four_dots<G>(d, sub, u_mine);
+        if (u_mine >= 0) dot_slots[base + r0 + u_mine] = f;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (e[u].off >= 0 && e[u].wgt != 0.f) {
+            float *gp = gvbase + e[u].off;
+#pragma unroll
+            for (int x = 0; x < V; x += 4)
+              red_add_v4(gp + x, e[u].wgt * go[x], e[u].wgt * go[x + 1], e[u].wgt * go[x + 2],
+                         e[u].wgt * go[x + 3]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    const float4 tq = reinterpret_cast<const float4 *>(dot_slots)[lane];
+    const float tt[4] = {tq.x, tq.y, tq.z, tq.w};
+    bwd_point_epilogue<DT, MODE>(a, c, j, st, tt);
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // any C: lanes stride over channels (correctness path for unusual widths)
 // ------------------------------------------------------------------------------------------------
 template <typename VT, typename DT, int MODE>
@@ -426,12 +547,43 @@ static void launch_backward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
   }
 }
 
+// Packed kernels: float storage, 16 / 32 / 64 channels, 4 / 8 / 16 points per item, every camera with the
+// same number of queries, locations and weights given by the caller.  Returns false otherwise.
+template <int MODE, int LP>
+static bool launch_backward_packed_c(const KArgs &a, dim3 grid, cudaStream_t s) {
+  switch (a.C) {
+    case 16: dfa3d_backward_packed_kernel<float, float, 16, MODE, LP><<<grid, kThreads, 0, s>>>(a); return true;
+    case 32: dfa3d_backward_packed_kernel<float, float, 32, MODE, LP><<<grid, kThreads, 0, s>>>(a); return true;
+    case 64: dfa3d_backward_packed_kernel<float, float, 64, MODE, LP><<<grid, kThreads, 0, s>>>(a); return true;
+    default: return false;
+  }
+}
+
+template <int MODE>
+static bool launch_backward_packed(const KArgs &a, int cams, cudaStream_t s) {
+  if (MODE == kCallerFused || a.q_off || (a.LP != 4 && a.LP != 8 && a.LP != 16)) return false;
+  const int per_cta = kWarpsPerCta * DFA3D_BWD_ITEMS_PER_WARP * (32 / a.LP);
+  const dim3 grid((unsigned)((a.items_per_cam + per_cta - 1) / per_cta), (unsigned)cams, 1);
+  constexpr int M = MODE == kCallerFused ? kFused : MODE;     // (never instantiated for caller-fused)
+  if (a.LP == 4) return launch_backward_packed_c<M, 4>(a, grid, s);
+  if (a.LP == 8) return launch_backward_packed_c<M, 8>(a, grid, s);
+  return launch_backward_packed_c<M, 16>(a, grid, s);
+}
+
+template <typename VT, typename DT> struct IsFloatPairB { static constexpr bool value = false; };
+template <> struct IsFloatPairB<float, float> { static constexpr bool value = true; };
+
 template <typename VT, typename DT, int MODE>
 static cudaError_t launch_backward_vd(const KArgs &a0, cudaStream_t s) {
   const bool full = a0.LP % 32 == 0;
   for (int b0 = 0; b0 < a0.B; b0 += 65535) {      // grid.y limit
     KArgs a = a0;
     a.b0 = b0;
+    if (IsFloatPairB<VT, DT>::value && launch_backward_packed<MODE>(a, min(65535, a0.B - b0), s)) {
+      const cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      continue;
+    }
     constexpr int kPerCta = kWarpsPerCta * DFA3D_BWD_ITEMS_PER_WARP;
     const dim3 grid((unsigned)((a.items_per_cam + kPerCta - 1) / kPerCta),
                     (unsigned)min(65535, a0.B - b0), 1);

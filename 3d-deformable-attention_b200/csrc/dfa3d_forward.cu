@@ -242,6 +242,106 @@ dfa3d_depth_score_forward_kernel(const KArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// few points per item (L*P = 4, 8 or 16): a warp takes 32 / (L*P) consecutive items at once
+// ------------------------------------------------------------------------------------------------
+// With one item per warp an item of 4 points (temporal self-attention and the decoder's cross-attention
+// use 1 level x 4 points) keeps 4 lanes busy in the prologue and costs a whole chain of dependent
+// latencies (locations -> row table -> rows -> sum -> store) for 16 rows.  Here lane j owns point
+// j % LP of item j / LP, so the prologue is full and coalesced (the points of consecutive items are
+// consecutive in memory); a group of G lanes then sums all rows of one item (or, when the warp holds
+// fewer items than groups, a share of them) and writes that item's output itself.
+template <typename VT, typename DT, int C, int MODE, bool WRITE_DS, int LP>
+__global__ void __launch_bounds__(kThreads, DFA3D_FWD_MIN_CTAS)
+dfa3d_forward_packed_kernel(const KArgs a) {
+  constexpr int V = RowVec<VT>::kElems;
+  constexpr int G = C / V;                      // lanes per row
+  constexpr int R = 32 / G;                     // groups per warp
+  constexpr int K = 32 / LP;                    // items per warp
+  constexpr int GPI = R > K ? R / K : 1;        // groups sharing one item
+  constexpr int IPG = K > R ? K / R : 1;        // items one group handles in turn
+  constexpr int U = 4;
+  constexpr int kRows = LP * 4;                 // rows of one item
+  static_assert(32 % LP == 0 && 32 % G == 0 && kRows % (GPI * U) == 0, "unsupported packing");
+  __shared__ LevelTable lv;
+  __shared__ __align__(16) RowEntry rows[kWarpsPerCta][128];
+  stage_levels(lv, a);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % G, grp = lane / G;
+  const int b = (int)blockIdx.y + a.b0;
+  const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)b * a.N * a.H * C + sub * V);
+  RowEntry *table = rows[warp];
+#pragma unroll 1
+  for (int it = 0; it < DFA3D_FWD_ITEMS_PER_WARP; ++it) {
+    const unsigned first = ((blockIdx.x * DFA3D_FWD_ITEMS_PER_WARP + it) * kWarpsPerCta + warp) * K;
+    if (first >= (unsigned)a.items_per_cam) return;
+    {
+      const unsigned idx = first + lane / LP;
+      const bool live = idx < (unsigned)a.items_per_cam;
+      ItemCtx c;
+      c.b = b;
+      const unsigned q = idx / (unsigned)a.H;
+      c.h = (int)(idx - q * (unsigned)a.H);
+      c.bq = (long long)b * a.Q + q;
+      c.item = (long long)b * a.items_per_cam + idx;
+      c.pt0 = c.item * LP;
+      c.loc = a.loc + c.pt0 * a.loc_stride;
+      c.attn = a.attn + c.pt0;
+      float ds[4], wgt[4];
+      int off[4];
+      const int j = lane % LP;
+      fwd_point<DT, MODE>(a, lv, c, live ? j : a.LP, SoftmaxStats{0.f, 1.f}, ds, wgt, off);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (off[k] >= 0) off[k] += c.h * C;     // rows of different heads share the table
+      store_rows(table, lane, off, wgt);
+      if (WRITE_DS && live)
+        reinterpret_cast<float4 *>(a.ds_out)[c.pt0 + j] = make_float4(ds[0], ds[1], ds[2], ds[3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int t = 0; t < IPG; ++t) {
+      const int i = grp / GPI + t * (R / GPI);  // item of the warp this group works on
+      const RowEntry *my = table + i * kRows + (grp % GPI) * U;
+      float acc[V];
+#pragma unroll
+      for (int x = 0; x < V; ++x) acc[x] = 0.f;
+#pragma unroll
+      for (int r0 = 0; r0 < kRows; r0 += GPI * U) {
+        RowEntry e[U];
+        float v[U][V];
+#pragma unroll
+        for (int u = 0; u < U; ++u) e[u] = my[r0 + u];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (e[u].off >= 0) {
+            RowVec<VT>::load(vbase + e[u].off, v[u]);
+          } else {
+#pragma unroll
+            for (int x = 0; x < V; ++x) v[u][x] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int x = 0; x < V; ++x) acc[x] = fmaf(e[u].wgt, v[u][x], acc[x]);
+      }
+#pragma unroll
+      for (int s = G; s < G * GPI; s <<= 1)
+#pragma unroll
+        for (int x = 0; x < V; ++x) acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], s);
+      const unsigned idx = first + i;
+      if (grp % GPI == 0 && idx < (unsigned)a.items_per_cam) {
+        float *o = a.out + (((long long)b * a.items_per_cam + idx) * C + sub * V);
+#pragma unroll
+        for (int x = 0; x < V; x += 4)
+          *reinterpret_cast<float4 *>(o + x) = make_float4(acc[x], acc[x + 1], acc[x + 2], acc[x + 3]);
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // host-side dispatch
 // ------------------------------------------------------------------------------------------------
 static dim3 item_grid(const KArgs &a, int cams, int items_per_warp) {
@@ -264,12 +364,49 @@ static void launch_forward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
   }
 }
 
+// Packed kernels: float storage, 16 / 32 / 64 channels, 4 / 8 / 16 points per item, every camera with the
+// same number of queries, locations and weights given by the caller.  Returns false when the call is not
+// one of those.
+template <int MODE, bool WRITE_DS, int LP>
+static bool launch_forward_packed_c(const KArgs &a, dim3 grid, cudaStream_t s) {
+  switch (a.C) {
+    case 16: dfa3d_forward_packed_kernel<float, float, 16, MODE, WRITE_DS, LP><<<grid, kThreads, 0, s>>>(a); return true;
+    case 32: dfa3d_forward_packed_kernel<float, float, 32, MODE, WRITE_DS, LP><<<grid, kThreads, 0, s>>>(a); return true;
+    case 64: dfa3d_forward_packed_kernel<float, float, 64, MODE, WRITE_DS, LP><<<grid, kThreads, 0, s>>>(a); return true;
+    default: return false;
+  }
+}
+
+template <int MODE>
+static bool launch_forward_packed(const KArgs &a, int cams, cudaStream_t s) {
+  if (MODE == kCallerFused || a.q_off || (a.LP != 4 && a.LP != 8 && a.LP != 16)) return false;
+  const int per_cta = kWarpsPerCta * DFA3D_FWD_ITEMS_PER_WARP * (32 / a.LP);
+  const dim3 grid((unsigned)((a.items_per_cam + per_cta - 1) / per_cta), (unsigned)cams, 1);
+  constexpr int M = MODE == kCallerFused ? kFused : MODE;     // (never instantiated for caller-fused)
+  if (a.ds_out) {
+    if (a.LP == 4) return launch_forward_packed_c<M, true, 4>(a, grid, s);
+    if (a.LP == 8) return launch_forward_packed_c<M, true, 8>(a, grid, s);
+    return launch_forward_packed_c<M, true, 16>(a, grid, s);
+  }
+  if (a.LP == 4) return launch_forward_packed_c<M, false, 4>(a, grid, s);
+  if (a.LP == 8) return launch_forward_packed_c<M, false, 8>(a, grid, s);
+  return launch_forward_packed_c<M, false, 16>(a, grid, s);
+}
+
+template <typename VT, typename DT> struct IsFloatPair { static constexpr bool value = false; };
+template <> struct IsFloatPair<float, float> { static constexpr bool value = true; };
+
 template <typename VT, typename DT, int MODE>
 static cudaError_t launch_forward_vd(const KArgs &a0, cudaStream_t s) {
   const bool full = a0.LP % 32 == 0;
   for (int b0 = 0; b0 < a0.B; b0 += 65535) {      // grid.y limit
     KArgs a = a0;
     a.b0 = b0;
+    if (IsFloatPair<VT, DT>::value && launch_forward_packed<MODE>(a, min(65535, a0.B - b0), s)) {
+      const cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      continue;
+    }
     const dim3 grid = item_grid(a, min(65535, a0.B - b0), DFA3D_FWD_ITEMS_PER_WARP);
     if (a.ds_out) {
       if (full) launch_forward_g<VT, DT, MODE, true, true>(a, grid, s);

@@ -697,6 +697,59 @@ def test_plain_2d_deformable_attention_matches_oracle(M, name):
     assert_close("grad_attn", attn.grad, ga, **BWD)
 
 
+PACKED_CASES = {
+    # L*P in {4, 8, 16} with 16 / 32 / 64 float channels: several items share a warp
+    "LP4_C32": dict(levels=((9, 7),), P=4, C=32, H=3, Q=37),
+    "LP4_C16": dict(levels=((9, 7),), P=4, C=16, H=5, Q=13),
+    "LP4_C64": dict(levels=((6, 5),), P=4, C=64, H=2, Q=21),
+    "LP8_C32": dict(levels=((9, 7), (4, 3)), P=4, C=32, H=3, Q=19),
+    "LP8_C16_one_level": dict(levels=((8, 8),), P=8, C=16, H=1, Q=50),
+    "LP16_C32": dict(levels=((9, 7), (4, 3), (2, 2), (1, 1)), P=4, C=32, H=3, Q=11),
+    "LP16_C16": dict(levels=((9, 7), (4, 3)), P=8, C=16, H=2, Q=9),
+    "LP16_C64": dict(levels=((9, 7), (4, 3)), P=8, C=64, H=1, Q=7),
+    "LP4_single_item": dict(levels=((3, 3),), P=4, C=32, H=1, Q=1),
+}
+
+
+@pytest.mark.parametrize("case", sorted(PACKED_CASES))
+def test_few_points_per_item_match_oracle(M, case):
+    """Items of 4, 8 or 16 points (temporal self-attention, decoder, single-level models) take kernels in
+    which a warp holds several items: one-stage operator, two-stage attention with a given depth score and
+    the plain 2-D operator against the oracle, item counts that do not fill the last warp."""
+    import dfa3d_oracle as O
+    w = wl.WORKLOADS["odd"].with_(name=case, seed=60 + len(case), D=6, **PACKED_CASES[case])
+    d = wl.make_inputs(w, head_repeat=True)
+    ref = oracle_all(d, np.float32)
+    for shared in (False, True):
+        check_against(run_fused(M, d, shared), ref, shared)
+    n = {k: v.numpy() for k, v in d.items()}
+    shapes2, loc2 = n["shapes"][:, :2], np.ascontiguousarray(n["loc"][..., :2])
+    # two-stage attention: depth scores given
+    o_out = O.wms_deform_attn_forward(n["value"], shapes2, n["lsi"], loc2, n["attn"], ref["ds"])
+    gv, gl2, ga, gds = O.wms_deform_attn_backward(n["value"], shapes2, n["lsi"], loc2, n["attn"], ref["ds"],
+                                                  n["grad_out"])
+    t = {k: v.to(DEV) for k, v in d.items()}
+    value, attn = t["value"].clone().requires_grad_(True), t["attn"].clone().requires_grad_(True)
+    loc = t["loc"][..., :2].contiguous().requires_grad_(True)
+    ds = torch.from_numpy(ref["ds"]).to(DEV).requires_grad_(True)
+    s2 = t["shapes"][:, :2].contiguous()
+    out = M.WeightedMultiScaleDeformableAttnFunction.apply(value, s2, t["lsi"], loc, attn, ds, 64)
+    out.backward(t["grad_out"])
+    for name, got, want in (("out", out, o_out), ("grad_value", value.grad, gv), ("grad_loc", loc.grad, gl2),
+                            ("grad_attn", attn.grad, ga), ("grad_ds", ds.grad, gds)):
+        assert_close("two-stage/" + name, got, want, **(FWD if name == "out" else BWD))
+    # plain 2-D operator
+    o = O.ms_deform_attn_forward(n["value"], shapes2, n["lsi"], loc2, n["attn"])
+    gv, gl, ga = O.ms_deform_attn_backward(n["value"], shapes2, n["lsi"], loc2, n["attn"], n["grad_out"])
+    value, attn = t["value"].clone().requires_grad_(True), t["attn"].clone().requires_grad_(True)
+    loc = t["loc"][..., :2].contiguous().requires_grad_(True)
+    out = M.MultiScaleDeformableAttnFunction.apply(value, s2, t["lsi"], loc, attn, 64)
+    out.backward(t["grad_out"])
+    for name, got, want in (("out", out, o), ("grad_value", value.grad, gv), ("grad_loc", loc.grad, gl),
+                            ("grad_attn", attn.grad, ga)):
+        assert_close("2d/" + name, got, want, **(FWD if name == "out" else BWD))
+
+
 def test_forward_backward_capture_into_a_cuda_graph(M):
     """The C-ABI calls only launch on the given stream (no allocation, no synchronisation), so a step
     on preallocated tensors can be captured once and replayed -- what a launch-bound small problem
