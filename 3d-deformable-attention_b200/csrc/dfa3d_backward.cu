@@ -337,29 +337,43 @@ dfa3d_backward_packed_kernel(const KArgs a) {
   float *gvbase = a.grad_value + cam;
   RowEntry *table = rows[warp];
   float *dot_slots = dots[warp];
+  // the camera's queries: rows [q0, q0 + nq) of the per-query tensors
+  const long long q0 = a.q_off ? (long long)__ldg(a.q_off + b) : (long long)b * a.Q;
+  const unsigned nitems = (unsigned)(a.q_off ? __ldg(a.q_off + b + 1) - (int)q0 : a.Q) * (unsigned)a.H;
 #pragma unroll 1
   for (int it = 0; it < DFA3D_BWD_ITEMS_PER_WARP; ++it) {
     const unsigned first = ((blockIdx.x * DFA3D_BWD_ITEMS_PER_WARP + it) * kWarpsPerCta + warp) * K;
-    if (first >= (unsigned)a.items_per_cam) return;
+    if (first >= nitems) return;
     const unsigned idx = first + lane / LP;
-    const bool live = idx < (unsigned)a.items_per_cam;
+    const bool live = idx < nitems;
     ItemCtx c;
     c.b = b;
     {
       const unsigned q = idx / (unsigned)a.H;
       c.h = (int)(idx - q * (unsigned)a.H);
-      c.bq = (long long)b * a.Q + q;
+      c.bq = q0 + q;
     }
-    c.item = (long long)b * a.items_per_cam + idx;
+    c.item = q0 * a.H + idx;
     c.pt0 = c.item * LP;
-    c.loc = a.loc + c.pt0 * a.loc_stride;
+    c.loc = a.loc + c.pt0 * a.loc_stride;        // (not dereferenced in caller-fused mode)
     c.attn = a.attn + c.pt0;
     const int j = live ? lane % LP : a.LP;       // a.LP: no such point, the lane stays idle
+    SoftmaxStats sm{0.f, 1.f};
+    if (MODE == kCallerFused) {                  // softmax over the item's LP logits: its own LP lanes
+      const float lg = live ? __ldg(a.logits + c.pt0 + j) : -INFINITY;
+      float mx = lg;
+#pragma unroll
+      for (int s = LP / 2; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+      float sum = live ? expf(lg - mx) : 0.f;
+#pragma unroll
+      for (int s = LP / 2; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+      sm = SoftmaxStats{mx, sum};
+    }
     PointState st;
     {
       float wgt[4];
       int off[4];
-      bwd_point<DT, MODE>(a, lv, c, j, SoftmaxStats{0.f, 1.f}, st, wgt, off);
+      bwd_point<DT, MODE>(a, lv, c, j, sm, st, wgt, off);
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         if (off[k] >= 0) off[k] += c.h * C;
@@ -372,8 +386,8 @@ dfa3d_backward_packed_kernel(const KArgs a) {
       const unsigned item_i = first + i;
       const int base = i * kRows + (grp % GPI) * U;
       float go[V];
-      if (item_i < (unsigned)a.items_per_cam) {
-        const float *gp = a.grad_out + (((long long)b * a.items_per_cam + item_i) * C + sub * V);
+      if (item_i < nitems) {
+        const float *gp = a.grad_out + ((q0 * a.H + item_i) * C + sub * V);
 #pragma unroll
         for (int x = 0; x < V; x += 4) {
           const float4 q4 = __ldg(reinterpret_cast<const float4 *>(gp + x));
@@ -423,7 +437,14 @@ dfa3d_backward_packed_kernel(const KArgs a) {
     __syncwarp();
     const float4 tq = reinterpret_cast<const float4 *>(dot_slots)[lane];
     const float tt[4] = {tq.x, tq.y, tq.z, tq.w};
-    bwd_point_epilogue<DT, MODE>(a, c, j, st, tt);
+    float part = bwd_point_epilogue<DT, MODE>(a, c, j, st, tt);
+    if (MODE == kCallerFused) {
+      // softmax backward, grad_logit_j = a_j * (g_j - sum_k a_k g_k): the sum runs over the item's LP lanes;
+      // g_j was parked in grad_logits by the epilogue
+#pragma unroll
+      for (int s = LP / 2; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
+      if (live) a.grad_logits[c.pt0 + j] = st.aw * (a.grad_logits[c.pt0 + j] - part);
+    }
     __syncwarp();
   }
 }
@@ -547,8 +568,7 @@ static void launch_backward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
   }
 }
 
-// Packed kernels: float storage, 16 / 32 / 64 channels, 4 / 8 / 16 points per item, every camera with the
-// same number of queries, locations and weights given by the caller.  Returns false otherwise.
+// Packed kernels: float storage, 16 / 32 / 64 channels, 4 / 8 / 16 points per item.  Returns false otherwise.
 template <int MODE, int LP>
 static bool launch_backward_packed_c(const KArgs &a, dim3 grid, cudaStream_t s) {
   switch (a.C) {
@@ -561,13 +581,12 @@ static bool launch_backward_packed_c(const KArgs &a, dim3 grid, cudaStream_t s) 
 
 template <int MODE>
 static bool launch_backward_packed(const KArgs &a, int cams, cudaStream_t s) {
-  if (MODE == kCallerFused || a.q_off || (a.LP != 4 && a.LP != 8 && a.LP != 16)) return false;
+  if (a.LP != 4 && a.LP != 8 && a.LP != 16) return false;
   const int per_cta = kWarpsPerCta * DFA3D_BWD_ITEMS_PER_WARP * (32 / a.LP);
   const dim3 grid((unsigned)((a.items_per_cam + per_cta - 1) / per_cta), (unsigned)cams, 1);
-  constexpr int M = MODE == kCallerFused ? kFused : MODE;     // (never instantiated for caller-fused)
-  if (a.LP == 4) return launch_backward_packed_c<M, 4>(a, grid, s);
-  if (a.LP == 8) return launch_backward_packed_c<M, 8>(a, grid, s);
-  return launch_backward_packed_c<M, 16>(a, grid, s);
+  if (a.LP == 4) return launch_backward_packed_c<MODE, 4>(a, grid, s);
+  if (a.LP == 8) return launch_backward_packed_c<MODE, 8>(a, grid, s);
+  return launch_backward_packed_c<MODE, 16>(a, grid, s);
 }
 
 template <typename VT, typename DT> struct IsFloatPairB { static constexpr bool value = false; };

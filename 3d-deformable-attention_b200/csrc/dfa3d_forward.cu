@@ -270,26 +270,40 @@ dfa3d_forward_packed_kernel(const KArgs a) {
   const int b = (int)blockIdx.y + a.b0;
   const VT *vbase = reinterpret_cast<const VT *>(a.value) + ((long long)b * a.N * a.H * C + sub * V);
   RowEntry *table = rows[warp];
+  // the camera's queries: rows [q0, q0 + nq) of the per-query tensors
+  const long long q0 = a.q_off ? (long long)__ldg(a.q_off + b) : (long long)b * a.Q;
+  const unsigned nitems = (unsigned)(a.q_off ? __ldg(a.q_off + b + 1) - (int)q0 : a.Q) * (unsigned)a.H;
 #pragma unroll 1
   for (int it = 0; it < DFA3D_FWD_ITEMS_PER_WARP; ++it) {
     const unsigned first = ((blockIdx.x * DFA3D_FWD_ITEMS_PER_WARP + it) * kWarpsPerCta + warp) * K;
-    if (first >= (unsigned)a.items_per_cam) return;
+    if (first >= nitems) return;
     {
       const unsigned idx = first + lane / LP;
-      const bool live = idx < (unsigned)a.items_per_cam;
+      const bool live = idx < nitems;
       ItemCtx c;
       c.b = b;
       const unsigned q = idx / (unsigned)a.H;
       c.h = (int)(idx - q * (unsigned)a.H);
-      c.bq = (long long)b * a.Q + q;
-      c.item = (long long)b * a.items_per_cam + idx;
+      c.bq = q0 + q;
+      c.item = q0 * a.H + idx;
       c.pt0 = c.item * LP;
-      c.loc = a.loc + c.pt0 * a.loc_stride;
+      c.loc = a.loc + c.pt0 * a.loc_stride;      // (not dereferenced in caller-fused mode)
       c.attn = a.attn + c.pt0;
+      const int j = lane % LP;
+      SoftmaxStats sm{0.f, 1.f};
+      if (MODE == kCallerFused) {                // softmax over the item's LP logits: its own LP lanes
+        const float lg = live ? __ldg(a.logits + c.pt0 + j) : -INFINITY;
+        float mx = lg;
+#pragma unroll
+        for (int s = LP / 2; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        float sum = live ? expf(lg - mx) : 0.f;
+#pragma unroll
+        for (int s = LP / 2; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+        sm = SoftmaxStats{mx, sum};
+      }
       float ds[4], wgt[4];
       int off[4];
-      const int j = lane % LP;
-      fwd_point<DT, MODE>(a, lv, c, live ? j : a.LP, SoftmaxStats{0.f, 1.f}, ds, wgt, off);
+      fwd_point<DT, MODE>(a, lv, c, live ? j : a.LP, sm, ds, wgt, off);
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         if (off[k] >= 0) off[k] += c.h * C;     // rows of different heads share the table
@@ -330,8 +344,8 @@ dfa3d_forward_packed_kernel(const KArgs a) {
 #pragma unroll
         for (int x = 0; x < V; ++x) acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], s);
       const unsigned idx = first + i;
-      if (grp % GPI == 0 && idx < (unsigned)a.items_per_cam) {
-        float *o = a.out + (((long long)b * a.items_per_cam + idx) * C + sub * V);
+      if (grp % GPI == 0 && idx < nitems) {
+        float *o = a.out + ((q0 * a.H + idx) * C + sub * V);
 #pragma unroll
         for (int x = 0; x < V; x += 4)
           *reinterpret_cast<float4 *>(o + x) = make_float4(acc[x], acc[x + 1], acc[x + 2], acc[x + 3]);
@@ -364,9 +378,8 @@ static void launch_forward_g(const KArgs &a, dim3 grid, cudaStream_t s) {
   }
 }
 
-// Packed kernels: float storage, 16 / 32 / 64 channels, 4 / 8 / 16 points per item, every camera with the
-// same number of queries, locations and weights given by the caller.  Returns false when the call is not
-// one of those.
+// Packed kernels: float storage, 16 / 32 / 64 channels, 4 / 8 / 16 points per item.  Returns false when the
+// call is not one of those.
 template <int MODE, bool WRITE_DS, int LP>
 static bool launch_forward_packed_c(const KArgs &a, dim3 grid, cudaStream_t s) {
   switch (a.C) {
@@ -379,18 +392,18 @@ static bool launch_forward_packed_c(const KArgs &a, dim3 grid, cudaStream_t s) {
 
 template <int MODE>
 static bool launch_forward_packed(const KArgs &a, int cams, cudaStream_t s) {
-  if (MODE == kCallerFused || a.q_off || (a.LP != 4 && a.LP != 8 && a.LP != 16)) return false;
+  if (a.LP != 4 && a.LP != 8 && a.LP != 16) return false;
   const int per_cta = kWarpsPerCta * DFA3D_FWD_ITEMS_PER_WARP * (32 / a.LP);
   const dim3 grid((unsigned)((a.items_per_cam + per_cta - 1) / per_cta), (unsigned)cams, 1);
-  constexpr int M = MODE == kCallerFused ? kFused : MODE;     // (never instantiated for caller-fused)
-  if (a.ds_out) {
-    if (a.LP == 4) return launch_forward_packed_c<M, true, 4>(a, grid, s);
-    if (a.LP == 8) return launch_forward_packed_c<M, true, 8>(a, grid, s);
-    return launch_forward_packed_c<M, true, 16>(a, grid, s);
+  constexpr bool kCanWriteDs = MODE != kCallerFused;          // the caller-fused entry points return no depth score
+  if (kCanWriteDs && a.ds_out) {
+    if (a.LP == 4) return launch_forward_packed_c<MODE, kCanWriteDs, 4>(a, grid, s);
+    if (a.LP == 8) return launch_forward_packed_c<MODE, kCanWriteDs, 8>(a, grid, s);
+    return launch_forward_packed_c<MODE, kCanWriteDs, 16>(a, grid, s);
   }
-  if (a.LP == 4) return launch_forward_packed_c<M, false, 4>(a, grid, s);
-  if (a.LP == 8) return launch_forward_packed_c<M, false, 8>(a, grid, s);
-  return launch_forward_packed_c<M, false, 16>(a, grid, s);
+  if (a.LP == 4) return launch_forward_packed_c<MODE, false, 4>(a, grid, s);
+  if (a.LP == 8) return launch_forward_packed_c<MODE, false, 8>(a, grid, s);
+  return launch_forward_packed_c<MODE, false, 16>(a, grid, s);
 }
 
 template <typename VT, typename DT> struct IsFloatPair { static constexpr bool value = false; };

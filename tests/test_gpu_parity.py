@@ -619,6 +619,10 @@ ATTN3D_CASES = {
     "LP32_Z4": dict(levels=((6, 5), (4, 4), (3, 3), (2, 3)), P=8, Z=4),
     "LP45_Z3_two_chunks": dict(levels=((6, 5), (4, 4), (3, 3), (2, 3), (1, 1)), P=9, Z=3),
     "C12_generic_Z1": dict(levels=((5, 7), (3, 4)), P=3, Z=1, C=12),
+    # several items per warp (L*P = 4 / 8 / 16 with 16 / 32 / 64 channels)
+    "packed_LP4_C32_Z2": dict(levels=((5, 7),), P=4, Z=2, C=32, H=3),
+    "packed_LP8_C16_Z4": dict(levels=((5, 7),), P=8, Z=4, C=16, H=5),
+    "packed_LP16_C64_Z4": dict(levels=((5, 7), (3, 4)), P=8, Z=4, C=64, H=1),
 }
 
 

@@ -130,10 +130,13 @@ def _per_camera_problem(w, lens, seed):
     return d, dense, packed, off, g
 
 
+@pytest.mark.parametrize("packed", [False, True], ids=["item_per_warp", "items_share_a_warp"])
 @pytest.mark.parametrize("lens", [[5, 0, 9, 2], [33], [0, 0, 4]])
-def test_ragged_fused_entry_points_match_dense_per_camera(M, lens):
+def test_ragged_fused_entry_points_match_dense_per_camera(M, lens, packed):
     from dfa3d_b200 import ext
     w = wl.WORKLOADS["odd"].with_(C=32)
+    if packed:                                   # L*P = 8: the kernels in which a warp holds 4 items
+        w = w.with_(levels=((9, 6), (4, 5)), P=4)
     d, dense, packed, off, _ = _per_camera_problem(w, lens, seed=5)
     t = {k: v.to(DEV) for k, v in d.items()}
     p = {k: v.to(DEV).contiguous() for k, v in packed.items()}
@@ -159,10 +162,13 @@ def test_ragged_fused_entry_points_match_dense_per_camera(M, lens):
         r0 += n
 
 
-def test_ragged_offsets_entry_points_match_dense_per_camera(M):
+@pytest.mark.parametrize("packed", [False, True], ids=["item_per_warp", "items_share_a_warp"])
+def test_ragged_offsets_entry_points_match_dense_per_camera(M, packed):
     from dfa3d_b200 import ext
     lens, Z = [7, 0, 12], 2
     w = wl.WORKLOADS["odd"].with_(C=32, P=4)
+    if packed:                                   # L*P = 16: the kernels in which a warp holds 2 items
+        w = w.with_(levels=((9, 6), (4, 5), (2, 2), (1, 1)))
     d, dense, packed, off, g = _per_camera_problem(w, lens, seed=9)
     R = sum(lens)
     ref = torch.rand(R, Z, 3, generator=g) * 1.2 - 0.1
