@@ -313,6 +313,8 @@ dfa3d_backward_kernel(const KArgs a) {
 // Lane j owns point j % LP of item j / LP (full, coalesced prologue and epilogue); a group of G lanes
 // walks the rows of one item -- or a share of them when the warp holds fewer items than groups -- with
 // that item's grad_out fragment.  Same row phase as backward_item otherwise.
+constexpr int kPackedRounds = 2;    // batches of 32 points a warp takes before its CTA retires
+
 template <typename VT, typename DT, int C, int MODE, int LP>
 __global__ void __launch_bounds__(kThreads, DFA3D_BWD_MIN_CTAS)
 dfa3d_backward_packed_kernel(const KArgs a) {
@@ -341,8 +343,8 @@ dfa3d_backward_packed_kernel(const KArgs a) {
   const long long q0 = a.q_off ? (long long)__ldg(a.q_off + b) : (long long)b * a.Q;
   const unsigned nitems = (unsigned)(a.q_off ? __ldg(a.q_off + b + 1) - (int)q0 : a.Q) * (unsigned)a.H;
 #pragma unroll 1
-  for (int it = 0; it < DFA3D_BWD_ITEMS_PER_WARP; ++it) {
-    const unsigned first = ((blockIdx.x * DFA3D_BWD_ITEMS_PER_WARP + it) * kWarpsPerCta + warp) * K;
+  for (int it = 0; it < kPackedRounds; ++it) {
+    const unsigned first = ((blockIdx.x * kPackedRounds + it) * kWarpsPerCta + warp) * K;
     if (first >= nitems) return;
     const unsigned idx = first + lane / LP;
     const bool live = idx < nitems;
@@ -582,7 +584,7 @@ static bool launch_backward_packed_c(const KArgs &a, dim3 grid, cudaStream_t s) 
 template <int MODE>
 static bool launch_backward_packed(const KArgs &a, int cams, cudaStream_t s) {
   if (a.LP != 4 && a.LP != 8 && a.LP != 16) return false;
-  const int per_cta = kWarpsPerCta * DFA3D_BWD_ITEMS_PER_WARP * (32 / a.LP);
+  const int per_cta = kWarpsPerCta * kPackedRounds * (32 / a.LP);
   const dim3 grid((unsigned)((a.items_per_cam + per_cta - 1) / per_cta), (unsigned)cams, 1);
   if (a.LP == 4) return launch_backward_packed_c<MODE, 4>(a, grid, s);
   if (a.LP == 8) return launch_backward_packed_c<MODE, 8>(a, grid, s);

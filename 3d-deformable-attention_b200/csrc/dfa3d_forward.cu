@@ -250,6 +250,10 @@ dfa3d_depth_score_forward_kernel(const KArgs a) {
 // j % LP of item j / LP, so the prologue is full and coalesced (the points of consecutive items are
 // consecutive in memory); a group of G lanes then sums all rows of one item (or, when the warp holds
 // fewer items than groups, a share of them) and writes that item's output itself.
+// A warp takes kPackedRounds batches of 32 points before its CTA retires (a batch is several items
+// here, so fewer rounds than DFA3D_FWD_ITEMS_PER_WARP keep the grid several waves deep at 40 000 queries).
+constexpr int kPackedRounds = 2;
+
 template <typename VT, typename DT, int C, int MODE, bool WRITE_DS, int LP>
 __global__ void __launch_bounds__(kThreads, DFA3D_FWD_MIN_CTAS)
 dfa3d_forward_packed_kernel(const KArgs a) {
@@ -274,8 +278,8 @@ dfa3d_forward_packed_kernel(const KArgs a) {
   const long long q0 = a.q_off ? (long long)__ldg(a.q_off + b) : (long long)b * a.Q;
   const unsigned nitems = (unsigned)(a.q_off ? __ldg(a.q_off + b + 1) - (int)q0 : a.Q) * (unsigned)a.H;
 #pragma unroll 1
-  for (int it = 0; it < DFA3D_FWD_ITEMS_PER_WARP; ++it) {
-    const unsigned first = ((blockIdx.x * DFA3D_FWD_ITEMS_PER_WARP + it) * kWarpsPerCta + warp) * K;
+  for (int it = 0; it < kPackedRounds; ++it) {
+    const unsigned first = ((blockIdx.x * kPackedRounds + it) * kWarpsPerCta + warp) * K;
     if (first >= nitems) return;
     {
       const unsigned idx = first + lane / LP;
@@ -393,7 +397,7 @@ static bool launch_forward_packed_c(const KArgs &a, dim3 grid, cudaStream_t s) {
 template <int MODE>
 static bool launch_forward_packed(const KArgs &a, int cams, cudaStream_t s) {
   if (a.LP != 4 && a.LP != 8 && a.LP != 16) return false;
-  const int per_cta = kWarpsPerCta * DFA3D_FWD_ITEMS_PER_WARP * (32 / a.LP);
+  const int per_cta = kWarpsPerCta * kPackedRounds * (32 / a.LP);
   const dim3 grid((unsigned)((a.items_per_cam + per_cta - 1) / per_cta), (unsigned)cams, 1);
   constexpr bool kCanWriteDs = MODE != kCallerFused;          // the caller-fused entry points return no depth score
   if (kCanWriteDs && a.ds_out) {

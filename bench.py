@@ -699,7 +699,37 @@ def measure_extras(a, w, dev, world, rank, barrier):
                          "forward_only_ms": f_ms, "forward_only_points_per_s": w3.points * world / (f_ms * 1e-3),
                          "fwd_bwd_ms": s_ms, "fwd_bwd_points_per_s": w3.points * world / (s_ms * 1e-3)}
         del r3
+        extra["few_points_per_item"] = measure_few_points(dev, world, barrier)
     return extra
+
+
+def measure_few_points(dev, world, barrier):
+    """The plain 2-D operator at the temporal self-attention shape (previous + current 200 x 200 BEV, 40 000
+    queries, 8 heads x 32 channels, 1 level x 4 points: items of 4 points, several per warp) and with 32
+    points per item (one item per warp) for comparison; same work on every rank, max over ranks."""
+    from dfa3d_b200 import ext
+    g = torch.Generator().manual_seed(7)
+    B, side, Q, H, C = 2, 200, 40000, 8, 32
+    shapes = torch.tensor([[side, side]], dtype=torch.int64, device=dev)
+    lsi = torch.zeros(1, dtype=torch.int64, device=dev)
+    value = torch.randn(B, side * side, H, C, generator=g).to(dev)
+    go = torch.randn(B, Q, H * C, generator=g).to(dev)
+    gv = torch.zeros_like(value)
+    out = {"shape": "2 maps of 200x200, 40 000 queries, 8 heads x 32 channels, 1 level, plain 2-D operator"}
+    for P in (4, 32):
+        loc = torch.rand(B, Q, H, 1, P, 2, generator=g).to(dev)
+        attn = torch.rand(B, Q, H, 1, P, generator=g).softmax(-1).to(dev)
+        gl, ga = torch.empty_like(loc), torch.empty_like(attn)
+        fwd = lambda i: ext.ms_deform_attn_forward(value, shapes, lsi, loc, attn, 64)
+        bwd = lambda i: ext.ms_deform_attn_backward(value, shapes, lsi, loc, attn, go, gv, gl, ga, 64)
+        for _ in range(3):
+            fwd(0); bwd(0)
+        f_ms, b_ms = _timed(fwd, 20, dev, world, barrier), _timed(bwd, 20, dev, world, barrier)
+        pts = B * Q * H * P
+        out[f"points_per_item_{P}"] = {"forward_ms": f_ms, "backward_ms": b_ms,
+                                       "forward_points_per_s": pts / (f_ms * 1e-3),
+                                       "backward_points_per_s": pts / (b_ms * 1e-3)}
+    return out
 
 
 def memory_stream_floor(w):
