@@ -754,6 +754,40 @@ def test_few_points_per_item_match_oracle(M, case):
         assert_close("2d/" + name, got, want, **(FWD if name == "out" else BWD))
 
 
+def test_temporal_self_attention_shape_at_full_size(M):
+    """The plain 2-D operator at the temporal self-attention shape (200 x 200 BEV, 40 000 queries, 8 heads x 32
+    channels, 1 level x 4 points: 8 items per warp): three slices of 256 queries -- first, middle, last --
+    against the oracle run on those queries alone (outputs and per-query gradients), and grad_value against
+    the oracle when only those queries carry an output gradient."""
+    import dfa3d_oracle as O
+    from dfa3d_b200 import ext
+    g = torch.Generator().manual_seed(77)
+    side, Q, H, C, P = 200, 40000, 8, 32, 4
+    shapes = torch.tensor([[side, side]], dtype=torch.int64)
+    lsi = torch.zeros(1, dtype=torch.int64)
+    value = torch.randn(1, side * side, H, C, generator=g)
+    loc = torch.rand(1, Q, H, 1, P, 2, generator=g) * 1.06 - 0.03
+    attn = torch.rand(1, Q, H, 1, P, generator=g)
+    picks = [slice(0, 256), slice(20000 - 128, 20000 + 128), slice(Q - 256, Q)]
+    go = torch.zeros(1, Q, H * C)
+    for sl in picks:
+        go[:, sl] = torch.randn(1, 256, H * C, generator=g)
+    dv, dl, da, dg = (t.to(DEV) for t in (value, loc, attn, go))
+    out = ext.ms_deform_attn_forward(dv, shapes.to(DEV), lsi.to(DEV), dl, da, 64)
+    gv = torch.zeros_like(dv); gl = torch.empty_like(dl); ga = torch.empty_like(da)
+    ext.ms_deform_attn_backward(dv, shapes.to(DEV), lsi.to(DEV), dl, da, dg, gv, gl, ga, 64)
+    want_gv = np.zeros(value.shape, dtype=np.float32)
+    for sl in picks:
+        l1, a1, g1 = (np.ascontiguousarray(t[:, sl].numpy()) for t in (loc, attn, go))
+        o = O.ms_deform_attn_forward(value.numpy(), shapes.numpy(), lsi.numpy(), l1, a1)
+        ogv, ogl, oga = O.ms_deform_attn_backward(value.numpy(), shapes.numpy(), lsi.numpy(), l1, a1, g1)
+        assert_close("out", out[:, sl], o, **FWD)
+        assert_close("grad_loc", gl[:, sl], ogl, **BWD)
+        assert_close("grad_attn", ga[:, sl], oga, **BWD)
+        want_gv += ogv
+    assert_close("grad_value", gv, want_gv, **BWD)
+
+
 def test_forward_backward_capture_into_a_cuda_graph(M):
     """The C-ABI calls only launch on the given stream (no allocation, no synchronisation), so a step
     on preallocated tensors can be captured once and replayed -- what a launch-bound small problem
