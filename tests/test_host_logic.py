@@ -220,3 +220,22 @@ def test_bev_reference_points_are_cell_and_pillar_centres():
             for k in range(n):
                 z = (0.5 + k * (Z - 1.0) / (n - 1)) / Z
                 assert torch.allclose(r3[0, k, q], torch.tensor([(x + 0.5) / W, (y + 0.5) / H, z]))
+
+
+def test_layer_ops_refuse_cpu_tensors_and_keep_torch_parameter_names():
+    """No fallback path: the row operations raise on CPU tensors; their modules keep torch's parameter names
+    so that checkpoints of the reference's LayerNorm / Linear layers load."""
+    import pytest
+    import torch
+    from dfa3d_b200.layer_ops import AddLayerNorm, Linear, column_sum, weight_gradient
+    with pytest.raises(RuntimeError, match="float32 CUDA"):
+        AddLayerNorm(128)(torch.zeros(2, 128))
+    with pytest.raises(RuntimeError, match="float32 CUDA"):
+        column_sum(torch.zeros(4, 8))
+    assert list(AddLayerNorm(64).state_dict()) == list(torch.nn.LayerNorm(64).state_dict())
+    assert list(Linear(8, 4).state_dict()) == list(torch.nn.Linear(8, 4).state_dict())
+    # the sliced weight gradient equals the plain product (CPU tensors: pure torch arithmetic)
+    g = torch.Generator().manual_seed(0)
+    go, x = torch.randn(16384 + 7, 12, generator=g), torch.randn(16384 + 7, 20, generator=g)
+    torch.testing.assert_close(weight_gradient(go, x), go.t() @ x, rtol=1e-4, atol=1e-3)
+    torch.testing.assert_close(weight_gradient(go[:100], x[:100]), go[:100].t() @ x[:100])
