@@ -769,13 +769,15 @@ def report(a, w, world, launches_per_step, value, ms_per_step, fwd_ms, bwd_ms, c
         "e2e": e2e,
     }
     if a.impl == "ours":
+        # items of 4 / 8 / 16 points (fp32, 16 / 32 / 64 channels) take the kernels in which a warp holds several
+        packed = w.L * w.P in (4, 8, 16) and w.C in (16, 32, 64) and w.value_dtype == "fp32"
         line["roofline"] = {
-            "kernel": "dfa3d_backward_kernel", "bound": "hbm",
+            "kernel": "dfa3d_backward_packed_kernel" if packed else "dfa3d_backward_kernel", "bound": "hbm",
             "achieved": bwd_b / (bwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
             "frac": bwd_b / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic.get("backward"),
             "algorithmic_bytes": bwd_b, "peak_source": peak_src}
         line["roofline_forward"] = {
-            "kernel": "dfa3d_forward_kernel", "bound": "hbm",
+            "kernel": "dfa3d_forward_packed_kernel" if packed else "dfa3d_forward_kernel", "bound": "hbm",
             "achieved": fwd_b / (fwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
             "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic.get("forward"),
             "algorithmic_bytes": fwd_b}
