@@ -754,6 +754,58 @@ def test_few_points_per_item_match_oracle(M, case):
         assert_close("2d/" + name, got, want, **(FWD if name == "out" else BWD))
 
 
+def test_random_small_item_shapes_match_oracle(M):
+    """Seeded random problems with 4 / 8 / 16 points per item (levels, heads, channels, cameras, query counts
+    drawn at random): one-stage operator with per-head and shared dist, and the caller-fused entry points,
+    against the oracle; ragged cameras bit-equal to the dense call on per-query outputs."""
+    import random
+    import dfa3d_oracle as O
+    from dfa3d_b200 import ext
+    rnd = random.Random(5)
+    for it in range(16):
+        LP = rnd.choice([4, 8, 16])
+        L = rnd.choice([x for x in (1, 2, 4) if LP % x == 0])
+        P = LP // L
+        Z = rnd.choice([z for z in (1, 2, 4) if P % z == 0])
+        w = wl.Workload(f"rnd{it}", B=rnd.randint(1, 3), levels=tuple((rnd.randint(1, 10), rnd.randint(1, 10))
+                                                                     for _ in range(L)),
+                        D=rnd.randint(1, 9), Q=rnd.randint(1, 90), P=P, H=rnd.randint(1, 7),
+                        C=rnd.choice([16, 32, 64]), seed=200 + it, oob=True)
+        d = wl.make_inputs(w, head_repeat=True)
+        ref = oracle_all(d, np.float32)
+        for shared in (False, True):
+            check_against(run_fused(M, d, shared), ref, shared)
+        g = torch.Generator().manual_seed(it)
+        ref_pts = torch.rand(w.B, w.Q, Z, 3, generator=g) * 1.2 - 0.1
+        off_uv = torch.randn(w.B, w.Q, w.H, w.L, w.P, 2, generator=g) * 1.5
+        off_d = torch.randn(w.B, w.Q, w.H, w.L, w.P, generator=g)
+        logits = torch.randn(w.B, w.Q, w.H, w.L * w.P, generator=g)
+        n = {k: v.numpy() for k, v in d.items()}
+        t = {k: v.to(DEV) for k, v in d.items()}
+        o_out = O.attn3d_forward(n["value"], n["dist"], n["shapes"], n["lsi"], ref_pts.numpy(), off_uv.numpy(),
+                                 off_d.numpy(), logits.numpy())
+        o_g = O.attn3d_backward(n["value"], n["dist"], n["shapes"], n["lsi"], ref_pts.numpy(), off_uv.numpy(),
+                                off_d.numpy(), logits.numpy(), n["grad_out"])
+        a = [x.to(DEV) for x in (ref_pts, off_uv, off_d, logits)]
+        out = ext.dfa3d_attn3d_forward(t["value"], t["dist"], t["shapes"], t["lsi"], *a)
+        gv = torch.zeros_like(t["value"]); gd = torch.zeros_like(t["dist"])
+        gs = [torch.empty_like(x) for x in a[1:]]
+        ext.dfa3d_attn3d_backward(t["value"], t["dist"], t["shapes"], t["lsi"], *a, t["grad_out"], gv, gd, *gs)
+        assert_close(f"{w.name}/out", out, o_out, **FWD)
+        for nm, got, want in zip(("grad_value", "grad_dist", "grad_off_uv", "grad_off_d", "grad_logits"),
+                                 (gv, gd, *gs), o_g):
+            assert_close(f"{w.name}/{nm}", got, want, **BWD)
+        lens = [rnd.randint(0, w.Q) for _ in range(w.B)]
+        if sum(lens) == 0:
+            continue
+        off = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
+        rows = lambda x: torch.cat([x[b, :lens[b]] for b in range(w.B)]).contiguous()
+        ro, rds = ext.dfa3d_fused_forward_ragged(t["value"], t["dist"], t["shapes"], t["lsi"], rows(t["loc"]),
+                                                 rows(t["attn"]), off, max(lens))
+        do, dds = ext.dfa3d_fused_forward(t["value"], t["dist"], t["shapes"], t["lsi"], t["loc"], t["attn"], 64)
+        assert torch.equal(ro, rows(do)) and torch.equal(rds, rows(dds)), w
+
+
 def test_temporal_self_attention_shape_at_full_size(M):
     """The plain 2-D operator at the temporal self-attention shape (200 x 200 BEV, 40 000 queries, 8 heads x 32
     channels, 1 level x 4 points: 8 items per warp): three slices of 256 queries -- first, middle, last --
