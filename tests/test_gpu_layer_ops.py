@@ -116,3 +116,28 @@ def test_layer_ops_compute_in_float32_under_autocast(lib_built):
     assert_close("autocast", got, want, rtol=5e-3, atol=5e-3)
     got.sum().backward()
     assert x.grad is not None and torch.isfinite(x.grad).all()
+
+
+def test_residual_block_gradients_match_torch(lib_built):
+    """A post-norm residual block as the encoder layer builds it -- norm(branch(q), q), twice, the residual
+    feeding its own branch -- against the same block on torch.nn.LayerNorm / torch.nn.Linear: the input
+    gradient (which sums the norm's gradient with the branch's) and every parameter gradient."""
+    from dfa3d_b200.layer_ops import AddLayerNorm, Linear
+    torch.manual_seed(11)
+    E, rows = 128, 301
+    mine = torch.nn.ModuleList([Linear(E, E), AddLayerNorm(E), Linear(E, E), AddLayerNorm(E)]).to(DEV)
+    ref = torch.nn.ModuleList([torch.nn.Linear(E, E), torch.nn.LayerNorm(E), torch.nn.Linear(E, E),
+                               torch.nn.LayerNorm(E)]).to(DEV)
+    ref.load_state_dict(mine.state_dict())
+    q0 = torch.randn(2, rows, E, device=DEV)
+    go = torch.randn(2, rows, E, device=DEV)
+
+    def run(m, fused):
+        q = q0.clone().requires_grad_(True)
+        x = m[1](m[0](q), q) if fused else m[1](m[0](q) + q)
+        y = m[3](torch.relu(m[2](x)), x) if fused else m[3](torch.relu(m[2](x)) + x)
+        y.backward(go)
+        return [y, q.grad] + [p.grad for p in m.parameters()]
+
+    for i, (a, b) in enumerate(zip(run(mine, True), run(ref, False))):
+        assert_close(f"tensor {i}", a, b, rtol=2e-4, atol_frac=2e-5)
