@@ -24,7 +24,7 @@ class HostPipeline:
     ``run(host_in, host_out)``: ``host_in`` maps value (B,N,H,C), dist (B,N,D) or (B,N,H,D),
     loc (B,Q,H,L,P,3), attn (B,Q,H,L,P), grad_out (B,Q,H*C) to pinned host tensors; ``host_out``
     maps out, grad_value, grad_dist, grad_loc, grad_attn to pinned host tensors that receive the
-    results.  value/dist may be bfloat16; all results are float32.
+    results.  value/dist may be bfloat16 or float16 (float16: both); all results are float32.
 
     Stream contract: all ``run()`` / ``join()`` calls of one pipeline must be issued from the same
     current stream (the pipeline orders its three side streams against that stream and against its own
