@@ -254,8 +254,13 @@ dfa3d_depth_score_forward_kernel(const KArgs a) {
 // here, so fewer rounds than DFA3D_FWD_ITEMS_PER_WARP keep the grid several waves deep at 40 000 queries).
 constexpr int kPackedRounds = 2;
 
+// CTAs per SM the packed forward is compiled for: 6 (48 warps; the kernel waits on chains of dependent
+// loads) measured 1-4 % faster than 5 and 4-8 % faster than 4 at 4, 8 and 16 points per item.
+#ifndef DFA3D_FWD_PACKED_MIN_CTAS
+#define DFA3D_FWD_PACKED_MIN_CTAS 6
+#endif
 template <typename VT, typename DT, int C, int MODE, bool WRITE_DS, int LP>
-__global__ void __launch_bounds__(kThreads, DFA3D_FWD_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, DFA3D_FWD_PACKED_MIN_CTAS)
 dfa3d_forward_packed_kernel(const KArgs a) {
   constexpr int V = RowVec<VT>::kElems;
   constexpr int G = C / V;                      // lanes per row
